@@ -14,7 +14,9 @@ Pool layout of a paged lane: ``[page][kv_head][slot][head_dim]`` for keys and th
 same for values, so one head's page is contiguous.
 
 Pages are given back when a request is closed and, in a windowed group, as soon
-as every position of a page is older than the window of the next query.
+as every position of a page is older than the window of the next query; in a group
+whose queries only see their own chunk, as soon as the next query's chunk starts
+behind the page.
 """
 from __future__ import annotations
 
@@ -46,7 +48,8 @@ class CacheLayout:
     def bytes_per_token(self, elt_bytes: int) -> int:
         """Key+value bytes one token adds over all paged lanes
         (the reference's arithmetic: src/cache/kv_budget.cpp:50-60)."""
-        return sum(2 * g.n_lanes * g.need.n_kv_heads * g.need.head_dim * elt_bytes for g in self.paged)
+        return sum(g.n_lanes * g.need.n_kv_heads * (g.need.head_dim + g.need.value_dim) * elt_bytes
+                   for g in self.paged)
 
     def bytes_per_request(self) -> int:
         total = 0
@@ -67,15 +70,21 @@ class KVLane:
         self.k, self.v, self.group, self.need, self.page_size = k, v, group, need, page_size
 
     def store(self, qkv, batch, q_out, n_heads: int, n_kv_heads: int, writes_cache: bool = True,
-              precise: bool = False) -> None:
-        """The lane's own write: from ``qkv`` ([T, (n_heads + 2 n_kv_heads) * head_dim], queries,
-        keys and values side by side, already position-encoded) the keys and values of token ``t``
+              precise: bool = False, bias=None) -> None:
+        """The lane's own write: from ``qkv`` ([T, n_heads * head_dim + n_kv_heads * (head_dim + value_dim)],
+        queries, keys and values side by side, already position-encoded) the keys and values of token ``t``
         go to page ``block_table[seq_of_token[t], p // page_size]``, slot ``p % page_size``
         (``p = batch.positions[t]``) and the queries to ``q_out``.  Nothing is rotated here, so a
-        position encoding never has to know how the cache is laid out."""
+        position encoding never has to know how the cache is laid out.  ``bias`` (32-bit, one entry per
+        column of ``qkv``) is added on the way; ``qkv`` may be 32-bit where the pools are not (one rounding)."""
         from ..csrc import ops
-        ops.rope_kv_write(qkv, batch.positions, batch.seq_of_token, batch.block_table(self.group), self.page_size,
-                          None, q_out, self.k, self.v, n_heads, n_kv_heads, self.need.head_dim, 0, writes_cache, precise)
+        table = batch.block_table(self.group)
+        if bias is None and self.need.value_dim == self.need.head_dim and qkv.dtype == self.k.dtype:
+            ops.rope_kv_write(qkv, batch.positions, batch.seq_of_token, table, self.page_size, None, q_out, self.k,
+                              self.v, n_heads, n_kv_heads, self.need.head_dim, 0, writes_cache, precise)
+        else:
+            ops.biased_kv_store(qkv, bias, batch.positions, batch.seq_of_token, table, self.page_size, q_out, self.k,
+                                self.v, n_heads, n_kv_heads, self.need.head_dim, self.need.value_dim, writes_cache)
 
 
 class StateLane:
@@ -105,9 +114,9 @@ class CacheManager:
         self._k: List[torch.Tensor] = []
         self._v: List[torch.Tensor] = []
         for g in layout.paged:
-            shape = (g.n_lanes, self.n_pages, g.need.n_kv_heads, page_size, g.need.head_dim)
-            self._k.append(torch.zeros(shape, dtype=dtype, device=device))
-            self._v.append(torch.zeros(shape, dtype=dtype, device=device))
+            shape = (g.n_lanes, self.n_pages, g.need.n_kv_heads, page_size)
+            self._k.append(torch.zeros(shape + (g.need.head_dim,), dtype=dtype, device=device))
+            self._v.append(torch.zeros(shape + (g.need.value_dim,), dtype=dtype, device=device))
         self._state = [torch.zeros((g.n_lanes, max_seqs) + tuple(g.need.shape),
                                    dtype=getattr(torch, getattr(g.need, "dtype", "float32")), device=device)
                        for g in layout.state]
@@ -135,10 +144,13 @@ class CacheManager:
 
     def _first_needed_block(self, g: int, length: int) -> int:
         """First logical block that the query at position ``length`` can still see."""
-        w = self.layout.paged[g].need.window
-        if w <= 0:
-            return 0
-        return max(0, length - w + 1) // self.page_size
+        need = self.layout.paged[g].need
+        first = 0
+        if need.window > 0:
+            first = max(first, length - need.window + 1)
+        if need.chunk > 0:
+            first = max(first, length // need.chunk * need.chunk)      # the start of that query's chunk
+        return first // self.page_size
 
     def pages_needed(self, seq: SequenceCache, n_new: int) -> List[int]:
         """New pages per group to hold ``n_new`` more tokens."""

@@ -140,12 +140,20 @@ class ModelConfig:
     def from_json(cls, j: Dict[str, Any]) -> "ModelConfig":  # pragma: no cover - overridden
         raise NotImplementedError
 
+    def with_tensor_shapes(self, shapes: Dict[str, tuple]) -> "ModelConfig":
+        """The configuration completed by what only the checkpoint's tensor shapes say (``shapes``:
+        tensor name -> shape).  Most architectures have every size in config.json and return self."""
+        return self
+
 
 def architecture_name(j: Dict[str, Any]) -> str:
+    """``architectures[0]`` (the usual list) or, where a config.json has it, the string ``architecture``."""
     archs = j.get("architectures")
-    if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: missing required field 'architectures' (a list naming the model class)")
-    return archs[0]
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    if isinstance(j.get("architecture"), str) and j["architecture"]:
+        return j["architecture"]
+    raise ConfigError("config.json: missing required field 'architectures' (a list naming the model class)")
 
 
 @dataclass(frozen=True)

@@ -58,5 +58,5 @@ def config_from_dir(model_dir: str) -> ModelConfig:
 
 
 def _ensure_builtin() -> None:
-    # the built-in architecture registers itself on import
-    from ..models import llama  # noqa: F401
+    # the built-in architectures register themselves on import
+    from ..models import llama, notirax  # noqa: F401

@@ -53,6 +53,20 @@ _SIGNATURES = {
     "mf_set_mid_rows_chunks": [c_int],
     "mf_mid_rows_max": [],
     "mf_mid_rows_linear": [_P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P],
+    "mf_embed_positions": [_P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
+    "mf_hyper_update_norm": [_P, _P, c_int, _P, _P, _P, _P, _P, c_float, c_int, _P, c_int, _P, c_int, c_int, c_int, _P],
+    "mf_attention_talking": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,
+                             c_float, c_float, _P, c_int, c_int, _P],
+    "mf_biased_kv_store": [_P, c_int, _P, _P, _P, _P, c_int, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
+                           c_int, c_int, _P],
+    "mf_delta_prepare": [_P, c_int, _P, c_int, _P, c_longlong, c_longlong, _P, _P, _P, _P, _P, _P, _P, _P, c_int,
+                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "mf_delta_gates": [_P, _P, _P, c_int, c_int, c_int, c_int, _P],
+    "mf_delta_recurrence": [_P, _P, _P, c_int, _P, c_longlong, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "mf_delta_output": [_P, _P, c_int, _P, c_float, _P, c_int, c_int, c_int, c_int, _P],
+    "mf_moe_route": [_P, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P],
+    "mf_moe_rows": [_P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float, c_float, _P],
+    "mf_moe_combine": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
 }
 
 MF_ERRORS = {10001: "a size or option this kernel does not take", 10002: "an unsupported dtype"}

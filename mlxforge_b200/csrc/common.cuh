@@ -139,6 +139,20 @@ enum MfKernel {
   MF_K_ATTN_DECODE_TMA,       // with tensor copies, a merge kernel after it
   MF_K_ATTN_DECODE_TMA_MERGED,  // with tensor copies, merging its splits itself
   MF_K_ATTN_DECODE_MERGE,
+  MF_K_EMBED_POSITIONS,       // embedding plus sinusoidal positions, into every residual stream
+  MF_K_HYPER_NORM,            // write-back into several residual streams, read-in and grouped RMS norm
+  MF_K_KV_STORE,              // projection biases and the cache write (key and value sizes may differ)
+  MF_K_ATTN_TALKING,          // attention with heads mixed before the softmax, a block per token
+  MF_K_ATTN_TALKING_TC,       // the same on tensor cores, a block per tile of queries
+  MF_K_DELTA_PREPARE,         // short convolutions, SiLU, unit norms of the delta rule's operands
+  MF_K_DELTA_GATES,
+  MF_K_DELTA_RECURRENCE,
+  MF_K_DELTA_OUTPUT,
+  MF_K_MOE_ROUTE,
+  MF_K_MOE_ROWS,              // experts for few tokens: a block per (token, chosen expert)
+  MF_K_MOE_COMBINE,
+  MF_K_MOE_SORT,              // (token, choice) pairs ordered by expert
+  MF_K_MOE_GROUPED,           // experts for many tokens: tensor-core tiles over the sorted pairs
   MF_K_COUNT
 };
 extern unsigned long long g_mf_kernel_launches[MF_K_COUNT];

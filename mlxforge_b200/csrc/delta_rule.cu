@@ -1,0 +1,277 @@
+// Gated delta rule with one decay per head and key channel, and what stands around it.
+//
+// Per head, with a state S [dim, vdim] in 32-bit that is carried from token to token:
+//   S <- diag(g_t) S ;  u = beta_t (v_t - S^T k_t) ;  S <- S + k_t u^T ;  o_t = S^T q_t
+// (the read-out sees the token's own write).  Queries and keys come from a short causal
+// convolution over time per channel and SiLU, are made unit vectors per head
+// (x / sqrt(sum x^2 + 1e-6)), the query also times dim^-1/2; values pass their own convolution
+// and SiLU.  g_t = exp(-exp(A_log_h) softplus(a_t + dt_bias)), beta_t = sigmoid(b_t).  The
+// read-out of a head is divided by its root mean square over vdim, multiplied by a weight and
+// by a sigmoid gate.  Everything after the projections is 32-bit.
+//
+// Every column of S is independent of the others: u_c = beta (v_c - S[:, c] . k) touches
+// column c only.  So the recurrence runs in parallel over (sequence, head, column) and is
+// serial in time only; a column is shared by 8 lanes that hold dim/8 rows each in registers.
+// The state after a token is the same however the prompt was cut: a step continues from the
+// state in the request's slot.
+//
+// The slot also keeps the last taps-1 inputs of the convolutions, [(taps-1), C] after S.
+#include "common.cuh"
+
+#define DR_LANES 8          // lanes that share a column of S
+#define DR_COLS 16          // columns per block
+#define DR_THREADS (DR_LANES * DR_COLS)
+
+__device__ __forceinline__ float dr_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float dr_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// ------------------------------------------------------------------ convolution, SiLU, unit norms, beta
+// proj [T, ld]: q | k | v channels (C of them), then n_heads beta logits, then `n_low` low-rank
+// activations that are only copied (rounded to the compute dtype) into `low` [T, n_low].
+// qkv_out [T, C] 32-bit: queries (unit, scaled), keys (unit), values.  beta_out [T, n_heads].
+template <typename TL>
+__global__ void __launch_bounds__(256)
+delta_prepare_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ conv_w, int taps,
+                     const float* __restrict__ state, long long state_stride, long long conv_off,
+                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                     const int* __restrict__ seq_q_start, const int* __restrict__ slots, float* __restrict__ qkv_out,
+                     float* __restrict__ beta_out, TL* __restrict__ low, int n_low, int n_heads, int n_kv, int dim,
+                     int vdim) {
+  extern __shared__ float y[];        // [C]
+  const int t = blockIdx.x;
+  const int C = 2 * n_kv * dim + n_heads * vdim;
+  const int seq = seq_of_token[t];
+  const int rel = t - seq_q_start[seq];           // index of the token within its portion
+  const float* tail = state + (long long)slots[seq] * state_stride + conv_off;   // [(taps-1), C]
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float a = 0.f;
+    for (int j = 0; j < taps; j++) {
+      const int back = taps - 1 - j;
+      float x;
+      if (rel - back >= 0) x = proj[(long long)(t - back) * ld + c];
+      else x = tail[(long long)(rel - back + taps - 1) * C + c];
+      a = fmaf(conv_w[(long long)c * taps + j], x, a);
+    }
+    y[c] = a * dr_sigmoid(a);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float* o = qkv_out + (long long)t * C;
+  // unit vectors: 2 * n_kv heads of `dim` channels, a warp each
+  for (int hh = warp; hh < 2 * n_kv; hh += nwarps) {
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32) ss = fmaf(y[hh * dim + d], y[hh * dim + d], ss);
+    ss = warp_sum(ss);
+    float inv = 1.0f / sqrtf(ss + 1e-6f);
+    if (hh < n_kv) inv *= 1.0f / sqrtf((float)dim);
+    for (int d = lane; d < dim; d += 32) o[hh * dim + d] = y[hh * dim + d] * inv;
+  }
+  for (int c = 2 * n_kv * dim + threadIdx.x; c < C; c += blockDim.x) o[c] = y[c];
+  const float* p = proj + (long long)t * ld;
+  for (int h = threadIdx.x; h < n_heads; h += blockDim.x) beta_out[(long long)t * n_heads + h] = dr_sigmoid(p[C + h]);
+  for (int i = threadIdx.x; i < n_low; i += blockDim.x) low[(long long)t * n_low + i] = from_f32<TL>(p[C + n_heads + i]);
+}
+
+// After the step the slot keeps the last taps-1 inputs of every channel.
+__global__ void delta_conv_tail_kernel(const float* __restrict__ proj, int ld, int C, int taps, float* __restrict__ state,
+                                       long long state_stride, long long conv_off, const int* __restrict__ seq_q_start,
+                                       const int* __restrict__ seq_q_len, const int* __restrict__ slots) {
+  const int seq = blockIdx.x;
+  const int start = seq_q_start[seq], n = seq_q_len[seq];
+  float* tail = state + (long long)slots[seq] * state_stride + conv_off;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    for (int j = 0; j < taps - 1; j++) {          // ascending: a read is never behind a write
+      const int src = n - (taps - 1) + j;
+      tail[(long long)j * C + c] = src >= 0 ? proj[(long long)(start + src) * ld + c] : tail[(long long)(j + n) * C + c];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ decays and output gates
+// ag [T, n_heads * dim + n_gate]: the first part becomes exp(-exp(A_log_h) softplus(x + dt_bias)),
+// the rest sigmoid(x), in place.
+__global__ void delta_gates_kernel(float* __restrict__ ag, const float* __restrict__ a_log,
+                                   const float* __restrict__ dt_bias, int n_decay, int dim, int width, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int j = (int)(i % width);
+  const float x = ag[i];
+  if (j < n_decay) ag[i] = expf(-expf(a_log[j / dim]) * dr_softplus(x + dt_bias[j]));
+  else ag[i] = dr_sigmoid(x);
+}
+
+// ------------------------------------------------------------------ the recurrence
+template <int DPT>
+__global__ void __launch_bounds__(DR_THREADS)
+delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ ag,
+                        int ag_ld, float* __restrict__ state, long long state_stride, const int* __restrict__ seq_q_start,
+                        const int* __restrict__ seq_q_len, const int* __restrict__ slots, float* __restrict__ o_out,
+                        int n_heads, int n_kv, int dim, int vdim) {
+  const int seq = blockIdx.x, h = blockIdx.y;
+  const int col = blockIdx.z * DR_COLS + threadIdx.x / DR_LANES;
+  const int part = threadIdx.x % DR_LANES;
+  const int kvh = h / (n_heads / n_kv);
+  const int C = 2 * n_kv * dim + n_heads * vdim;
+  const int start = seq_q_start[seq], n = seq_q_len[seq];
+  const bool live = col < vdim;
+  float* S = state + (long long)slots[seq] * state_stride + (long long)h * dim * vdim;
+  float s[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; i++) {
+    const int d = part * DPT + i;
+    s[i] = (live && d < dim) ? S[(long long)d * vdim + col] : 0.f;
+  }
+  float kd[DPT], qd[DPT], gd[DPT];
+  float v = 0.f, b = 0.f;
+  auto fetch = [&](int t) {
+    const float* row = qkv + (long long)t * C;
+#pragma unroll
+    for (int i = 0; i < DPT; i++) {
+      const int d = part * DPT + i;
+      const bool in = d < dim;
+      qd[i] = in ? row[kvh * dim + d] : 0.f;
+      kd[i] = in ? row[n_kv * dim + kvh * dim + d] : 0.f;
+      gd[i] = in ? ag[(long long)t * ag_ld + h * dim + d] : 0.f;
+    }
+    v = live ? row[2 * n_kv * dim + h * vdim + col] : 0.f;
+    b = beta[(long long)t * n_heads + h];
+  };
+  if (n > 0) fetch(start);
+  for (int t = start; t < start + n; t++) {
+    float kc[DPT], qc[DPT], gc[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; i++) {
+      kc[i] = kd[i];
+      qc[i] = qd[i];
+      gc[i] = gd[i];
+    }
+    const float vc = v, bc = b;
+    if (t + 1 < start + n) fetch(t + 1);          // the next token's operands are on their way meanwhile
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPT; i++) {
+      s[i] *= gc[i];
+      dot = fmaf(s[i], kc[i], dot);
+    }
+#pragma unroll
+    for (int off = 1; off < DR_LANES; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    const float u = bc * (vc - dot);
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPT; i++) {
+      s[i] = fmaf(kc[i], u, s[i]);
+      o = fmaf(s[i], qc[i], o);
+    }
+#pragma unroll
+    for (int off = 1; off < DR_LANES; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+    if (live && part == 0) o_out[(long long)t * n_heads * vdim + h * vdim + col] = o;
+  }
+#pragma unroll
+  for (int i = 0; i < DPT; i++) {
+    const int d = part * DPT + i;
+    if (live && d < dim) S[(long long)d * vdim + col] = s[i];
+  }
+}
+
+// ------------------------------------------------------------------ read-out norm and gate
+// out[t, h, c] = o[t, h, c] / sqrt(mean_c o^2 + eps) * w[c] * gate[t, h, c]; a warp per (token, head).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+delta_output_kernel(const float* __restrict__ o, const float* __restrict__ gate, int gate_ld,
+                    const float* __restrict__ w, float eps, TO* __restrict__ out, int n_heads, int vdim, int total) {
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= total) return;
+  const int lane = threadIdx.x & 31;
+  const int t = item / n_heads, h = item - t * n_heads;
+  const float* row = o + (long long)item * vdim;
+  float ss = 0.f;
+  for (int c = lane; c < vdim; c += 32) ss = fmaf(row[c], row[c], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+  const float* g = gate + (long long)t * gate_ld + h * vdim;
+  for (int c = lane; c < vdim; c += 32) out[(long long)item * vdim + c] = from_f32<TO>(row[c] * inv * w[c] * g[c]);
+}
+
+// ------------------------------------------------------------------ entry points
+MF_API int mf_delta_prepare(const float* proj, int ld, const float* conv_w, int taps, float* state,
+                            long long state_stride, long long conv_off, const int* positions, const int* seq_of_token,
+                            const int* seq_q_start, const int* seq_q_len, const int* slots, float* qkv_out,
+                            float* beta_out, void* low, int low_dtype, int n_low, int T, int n_seqs, int n_heads,
+                            int n_kv, int dim, int vdim, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (taps < 1 || n_kv <= 0 || n_heads % n_kv) return MF_ERR_BAD_ARG;
+  const int C = 2 * n_kv * dim + n_heads * vdim;
+  const size_t smem = (size_t)C * sizeof(float);
+  if (smem > 200 * 1024) return MF_ERR_BAD_ARG;
+  mf_count(MF_K_DELTA_PREPARE);
+#define DP_LAUNCH(TL)                                                                                              \
+  do {                                                                                                             \
+    if (smem > 48 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(delta_prepare_kernel<TL>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                           (int)smem);                                                             \
+      if (e != cudaSuccess) return (int)e;                                                                         \
+    }                                                                                                              \
+    delta_prepare_kernel<TL><<<T, 256, smem, stream>>>(proj, ld, conv_w, taps, state, state_stride, conv_off,      \
+                                                       positions, seq_of_token, seq_q_start, slots, qkv_out,       \
+                                                       beta_out, (TL*)low, n_low, n_heads, n_kv, dim, vdim);       \
+  } while (0)
+  if (low_dtype == MF_F32) DP_LAUNCH(float);
+  else if (low_dtype == MF_BF16) DP_LAUNCH(__nv_bfloat16);
+  else return MF_ERR_BAD_DTYPE;
+#undef DP_LAUNCH
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  if (taps > 1) {
+    delta_conv_tail_kernel<<<n_seqs, 256, 0, stream>>>(proj, ld, C, taps, state, state_stride, conv_off, seq_q_start,
+                                                       seq_q_len, slots);
+    e = cudaGetLastError();
+  }
+  return (int)e;
+}
+
+MF_API int mf_delta_gates(float* ag, const float* a_log, const float* dt_bias, int T, int n_heads, int dim, int n_gate,
+                          cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int width = n_heads * dim + n_gate;
+  const long long total = (long long)T * width;
+  mf_count(MF_K_DELTA_GATES);
+  delta_gates_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(ag, a_log, dt_bias, n_heads * dim, dim, width,
+                                                                         total);
+  return (int)cudaGetLastError();
+}
+
+MF_API int mf_delta_recurrence(const float* qkv, const float* beta, const float* ag, int ag_ld, float* state,
+                               long long state_stride, const int* seq_q_start, const int* seq_q_len, const int* slots,
+                               float* o_out, int n_seqs, int n_heads, int n_kv, int dim, int vdim, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (dim <= 0 || dim > 32 * DR_LANES || n_kv <= 0 || n_heads % n_kv || n_heads > 65535) return MF_ERR_BAD_ARG;
+  dim3 grid(n_seqs, n_heads, (vdim + DR_COLS - 1) / DR_COLS);
+  mf_count(MF_K_DELTA_RECURRENCE);
+#define DR_LAUNCH(DPT)                                                                                             \
+  delta_recurrence_kernel<DPT><<<grid, DR_THREADS, 0, stream>>>(qkv, beta, ag, ag_ld, state, state_stride,         \
+                                                                seq_q_start, seq_q_len, slots, o_out, n_heads, n_kv, \
+                                                                dim, vdim)
+  const int per = (dim + DR_LANES - 1) / DR_LANES;
+  if (per <= 4) DR_LAUNCH(4);
+  else if (per <= 8) DR_LAUNCH(8);
+  else if (per <= 16) DR_LAUNCH(16);
+  else DR_LAUNCH(32);
+#undef DR_LAUNCH
+  return (int)cudaGetLastError();
+}
+
+MF_API int mf_delta_output(const float* o, const float* gate, int gate_ld, const float* w, float eps, void* out,
+                           int out_dtype, int T, int n_heads, int vdim, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int total = T * n_heads;
+  const unsigned blocks = (unsigned)((total + 7) / 8);
+  mf_count(MF_K_DELTA_OUTPUT);
+  if (out_dtype == MF_F32)
+    delta_output_kernel<float><<<blocks, 256, 0, stream>>>(o, gate, gate_ld, w, eps, (float*)out, n_heads, vdim, total);
+  else if (out_dtype == MF_BF16)
+    delta_output_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(o, gate, gate_ld, w, eps, (__nv_bfloat16*)out,
+                                                                   n_heads, vdim, total);
+  else
+    return MF_ERR_BAD_DTYPE;
+  return (int)cudaGetLastError();
+}

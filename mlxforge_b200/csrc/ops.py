@@ -364,3 +364,137 @@ def set_dependent_launch(on: bool) -> bool:
     """Switch programmatic dependent launch of the decode-path kernels on or off;
     returns the previous setting.  Results do not depend on it."""
     return bool(library().mf_set_pdl(1 if on else 0))
+
+
+# ---------------------------------------------------------------------------- residual streams, grouped norm
+
+def embed_positions(table: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor,
+                    freqs: Optional[torch.Tensor], out: torch.Tensor, copies: int, precise: bool) -> None:
+    """out [T, copies, H] (32-bit) = table[token] + sinusoid(position), the same in every copy.
+    ``freqs``: float64 [ceil(H/2)], or None for no position vector."""
+    _need_cuda(table, tokens, positions, freqs, out)
+    T = tokens.shape[0]
+    H = table.shape[1]
+    if freqs is not None and (freqs.dtype != torch.float64 or freqs.numel() < (H + 1) // 2):
+        raise KernelError("embed_positions: freqs must be float64 [ceil(H/2)]")
+    check(library().mf_embed_positions(table.data_ptr(), dtype_code(table), tokens.data_ptr(), positions.data_ptr(),
+                                       _ptr(freqs), out.data_ptr(), T, H, copies, int(precise), _stream()),
+          "embed_positions")
+
+
+def hyper_update_norm(streams: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Optional[torch.Tensor],
+                      mix: Optional[torch.Tensor], w_out: Optional[torch.Tensor], w_in: Optional[torch.Tensor],
+                      weight: torch.Tensor, eps: float, groups: int, out: torch.Tensor, n_streams: int,
+                      rows: Optional[torch.Tensor] = None) -> None:
+    """Write ``delta`` back into the streams (``x_t <- sum_s mix[s, t] x_s + w_out[t] (delta + bias)``), read
+    them (``u = sum_s w_in[s] x_s``) and normalise ``u`` in ``groups`` groups.  ``streams`` is [T, S * H]
+    32-bit; with ``rows`` only those rows are produced and the streams stay as they are."""
+    _need_cuda(streams, delta, delta_bias, mix, w_out, w_in, weight, out, rows)
+    H = out.shape[-1]
+    n = out.shape[0]
+    check(library().mf_hyper_update_norm(streams.data_ptr(), _ptr(delta), dtype_code(delta) if delta is not None else
+                                         dtype_code(out), _ptr(delta_bias), _ptr(mix), _ptr(w_out), _ptr(w_in),
+                                         weight.data_ptr(), eps, groups, out.data_ptr(), dtype_code(out), _ptr(rows),
+                                         n, H, n_streams, _stream()), "hyper_update_norm")
+
+
+# ---------------------------------------------------------------------------- attention with talking heads
+
+def biased_kv_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+                    seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int, q_out: torch.Tensor,
+                    k_pool: torch.Tensor, v_pool: torch.Tensor, n_heads: int, n_kv: int, dim: int, vdim: int,
+                    write_kv: bool) -> None:
+    _need_cuda(qkv, bias, positions, seq_of_token, block_table, q_out, k_pool, v_pool)
+    check(library().mf_biased_kv_store(qkv.data_ptr(), dtype_code(qkv), _ptr(bias), positions.data_ptr(),
+                                       seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                                       page_size, q_out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+                                       dtype_code(q_out), qkv.shape[0], n_heads, n_kv, dim, vdim, int(write_kv),
+                                       _stream()), "biased_kv_store")
+
+
+def attention_talking(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                      positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                      n_heads: int, n_kv: int, dim: int, vdim: int, scale: float, softcap: float,
+                      talk: Optional[torch.Tensor], window: int, chunk: int) -> None:
+    _need_cuda(q, k_pool, v_pool, out, positions, seq_of_token, block_table, talk)
+    check(library().mf_attention_talking(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+                                         dtype_code(q), q.shape[0], n_heads, n_kv, dim, vdim, positions.data_ptr(),
+                                         seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                                         page_size, scale, softcap, _ptr(talk), window, chunk, _stream()),
+          "attention_talking")
+
+
+# ---------------------------------------------------------------------------- gated delta rule
+
+def delta_prepare(proj: torch.Tensor, conv_w: torch.Tensor, taps: int, state: torch.Tensor, conv_off: int,
+                  batch, qkv_out: torch.Tensor, beta_out: torch.Tensor, low: torch.Tensor, n_heads: int, n_kv: int,
+                  dim: int, vdim: int) -> None:
+    """Convolutions, SiLU and unit norms of the step's projections; the slots' convolution tails move on."""
+    _need_cuda(proj, conv_w, state, qkv_out, beta_out, low)
+    check(library().mf_delta_prepare(proj.data_ptr(), proj.shape[1], conv_w.data_ptr(), taps, state.data_ptr(),
+                                     state.stride(0), conv_off, batch.positions.data_ptr(),
+                                     batch.seq_of_token.data_ptr(), batch.seq_q_start.data_ptr(),
+                                     batch.seq_q_len.data_ptr(), batch.slots.data_ptr(), qkv_out.data_ptr(),
+                                     beta_out.data_ptr(), low.data_ptr(), dtype_code(low), low.shape[1],
+                                     proj.shape[0], batch.n_seqs, n_heads, n_kv, dim, vdim, _stream()),
+          "delta_prepare", launches=2 if taps > 1 else 1)
+
+
+def delta_gates(ag: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, n_heads: int, dim: int,
+                n_gate: int) -> None:
+    _need_cuda(ag, a_log, dt_bias)
+    check(library().mf_delta_gates(ag.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), ag.shape[0], n_heads, dim,
+                                   n_gate, _stream()), "delta_gates")
+
+
+def delta_recurrence(qkv: torch.Tensor, beta: torch.Tensor, ag: torch.Tensor, state: torch.Tensor, batch,
+                     o_out: torch.Tensor, n_heads: int, n_kv: int, dim: int, vdim: int) -> None:
+    _need_cuda(qkv, beta, ag, state, o_out)
+    check(library().mf_delta_recurrence(qkv.data_ptr(), beta.data_ptr(), ag.data_ptr(), ag.shape[1], state.data_ptr(),
+                                        state.stride(0), batch.seq_q_start.data_ptr(), batch.seq_q_len.data_ptr(),
+                                        batch.slots.data_ptr(), o_out.data_ptr(), batch.n_seqs, n_heads, n_kv, dim,
+                                        vdim, _stream()), "delta_recurrence")
+
+
+def delta_output(o: torch.Tensor, gate: torch.Tensor, gate_ld: int, weight: torch.Tensor, eps: float,
+                 out: torch.Tensor, n_heads: int, vdim: int) -> None:
+    """``gate`` points at the first gate of the first token; rows are ``gate_ld`` floats apart."""
+    _need_cuda(o, weight, out)
+    check(library().mf_delta_output(o.data_ptr(), gate.data_ptr(), gate_ld, weight.data_ptr(), eps, out.data_ptr(),
+                                    dtype_code(out), o.shape[0], n_heads, vdim, _stream()), "delta_output")
+
+
+# ---------------------------------------------------------------------------- mixture of experts
+
+def moe_route(z: torch.Tensor, n_groups: int, keep: int, top: int, route_scale: float, ids: torch.Tensor,
+              weights: torch.Tensor) -> None:
+    _need_cuda(z, ids, weights)
+    check(library().mf_moe_route(z.data_ptr(), z.shape[0], z.shape[1], n_groups, keep, top, route_scale,
+                                 ids.data_ptr(), weights.data_ptr(), _stream()), "moe_route")
+
+
+def moe_rows(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, y: torch.Tensor,
+             limit: float, alpha: float) -> None:
+    """y [T, top, H] (32-bit) = each chosen expert's output for its token, not yet weighted."""
+    _need_cuda(x, w_gu, w_down, ids, y)
+    T, H = x.shape
+    check(library().mf_moe_rows(x.data_ptr(), w_gu.data_ptr(), w_down.data_ptr(), dtype_code(x), ids.data_ptr(),
+                                y.data_ptr(), T, H, w_down.shape[2], ids.shape[1], limit, alpha, _stream()),
+          "moe_rows")
+
+
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, slot_of: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    _need_cuda(y, weights, slot_of, out)
+    T, H = out.shape
+    check(library().mf_moe_combine(y.data_ptr(), weights.data_ptr(), _ptr(slot_of), out.data_ptr(), dtype_code(out),
+                                   T, H, weights.shape[1], _stream()), "moe_combine")
+
+
+def attention_talking_tc_ok(n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int) -> bool:
+    """Whether the tensor-core kernel for portions of prompts takes these sizes."""
+    return False
+
+
+def moe_grouped_ok(hidden: int, ff: int) -> bool:
+    """Whether the sorted, tiled expert path takes these sizes."""
+    return False

@@ -12,6 +12,7 @@ import torch
 from ..config.model_config import apply_rope_scaling_override, read_config_json
 from ..config.registry import config_from_json, get_architecture
 from ..models.decoder import DecoderModel
+from ..weights.loader import tensor_shapes
 from .runtime import Runtime
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -43,7 +44,7 @@ def load_model(model_dir: str, dtype="bfloat16", device: str = "cuda",
     j = read_config_json(model_dir)
     if rope_scaling:
         j = apply_rope_scaling_override(j, rope_scaling)
-    config = config_from_json(j)
+    config = config_from_json(j).with_tensor_shapes(tensor_shapes(model_dir))
     arch = get_architecture(config.architecture)
     rt = Runtime(parse_dtype(dtype), device)
     model = DecoderModel(arch.build_spec(config), rt)

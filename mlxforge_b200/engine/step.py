@@ -85,7 +85,7 @@ class ModelRunner:
         self.last_meta_bytes = 0
         self.steps = 0
         self._last: Optional[dict] = None     # the last decode-only step's metadata, for _advance
-        self._plain_groups = all(g.need.window == 0 for g in cache.layout.paged)
+        self._plain_groups = all(g.need.window == 0 and g.need.chunk == 0 for g in cache.layout.paged)
         # CUDA graphs of decode-only steps, keyed by the shape of the step's metadata
         self._graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
         self.max_graphs = 256

@@ -29,6 +29,9 @@ class DecoderModel:
             if item.cache_of is not None and not (0 <= item.cache_of < i):
                 raise ValueError(f"schedule item {i} reads the cache of item {item.cache_of}, which does not run before it")
         self.cache_layout = self._layout()
+        # called after every run of a layer with (item, stream tensor, pending write), if set: how a
+        # test reads the residual stream between layers
+        self.probe = None
 
     # ------------------------------------------------------------------ weights
     def parts(self):
@@ -88,7 +91,8 @@ class DecoderModel:
                 if src is None or src[0] != "paged":
                     raise ValueError(f"schedule item {i} reads the cache of item {item.cache_of}, which has none to share")
                 src_need = paged[src[1]][0]
-                if not isinstance(need, PagedKV) or (need.n_kv_heads, need.head_dim) != (src_need.n_kv_heads, src_need.head_dim):
+                if not isinstance(need, PagedKV) or (need.n_kv_heads, need.head_dim, need.value_dim) != (
+                        src_need.n_kv_heads, src_need.head_dim, src_need.value_dim):
                     raise ValueError(f"schedule item {i} cannot read a cache of another geometry")
                 item_lane.append(src)
                 continue
@@ -125,12 +129,14 @@ class DecoderModel:
         was asked for)."""
         rt = self.rt
         T = batch.n_tokens
-        residual = rt.buffer("residual", (T, self.spec.hidden_size), torch.float32)
-        self.embedding.forward(batch.tokens, residual)
+        residual = rt.buffer("residual", (T, self.spec.streams * self.spec.hidden_size), torch.float32)
+        self.embedding.embed(batch, residual, self.spec.streams)
         pending = None
         for i, item in enumerate(self.spec.schedule):
             residual, pending = self.blocks[item.layer].forward(
                 residual, pending, batch, cache.lane(i), writes_cache=item.cache_of is None)
+            if self.probe is not None:
+                self.probe(i, residual, pending)
         if batch.n_wanted == 0:
             return None
         hn = self.final_norm.add_forward(residual, pending, rows=batch.want_rows,

@@ -43,8 +43,8 @@ class LayerSpec:
     The four usual roles have fields of their own; any of them may be None (a layer
     without a feed-forward, an arrangement with one norm).  ``extra`` holds further
     parts as ``(role, family, spec)``, ``family`` being the registry the part is
-    built from: "mixer", "feed_forward" or "norm" (a norm after the mixer, a second
-    feed-forward, ...).  The arrangement finds all of them under their roles."""
+    built from: "mixer", "feed_forward", "norm" or "connection" (a norm after the mixer,
+    a second feed-forward, the connections of a layer with several residual streams, ...).  The arrangement finds all of them under their roles."""
 
     block: str                     # arrangement kind, e.g. "prenorm"
     mixer: Optional[PartSpec] = None
@@ -88,6 +88,10 @@ class ModelSpec:
     head: PartSpec
     eos_token_ids: Tuple[int, ...] = ()
     max_position_embeddings: int = 0
+    # residual streams per token (1: the ordinary residual).  With more, the stream tensor that
+    # travels through the blocks is [T, streams * hidden_size] and the arrangement, its
+    # connections and the norms say how the streams are read and written.
+    streams: int = 1
 
 
 @dataclass(frozen=True)
@@ -107,11 +111,20 @@ class TensorSpec:
 class PagedKV:
     """Keys and values that grow with the sequence, kept in pages.  ``window`` > 0
     means a run only ever reads the last ``window`` positions, so older pages are
-    given back."""
+    given back.  ``chunk`` > 0 means a query only reads keys of its own chunk
+    (``floor(j / chunk) == floor(i / chunk)``), so the pages before the chunk of the
+    next query are given back too.  ``v_head_dim`` > 0: values have another size than
+    keys (0: the same)."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    chunk: int = 0
+    v_head_dim: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -213,6 +226,12 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Connection(Part):
+    """How a sublayer is joined to the residual stream(s): the weights with which the
+    streams are read for it and with which its result is written back.  An arrangement
+    that has several streams asks its connections for them."""
+
+
 class Block:
     """Arrangement of a layer's parts around the residual stream.  The stream
     travels as ``(residual, pending)``: ``pending`` is a delta not yet added, so
@@ -279,6 +298,7 @@ FEED_FORWARDS = _Registry("feed-forward")
 NORMS = _Registry("norm")
 POSITIONS = _Registry("position encoding")
 BLOCKS = _Registry("block arrangement")
+CONNECTIONS = _Registry("stream connection")
 EMBEDDINGS = _Registry("embedding")
 HEADS = _Registry("output head")
 
@@ -287,6 +307,7 @@ register_feed_forward = FEED_FORWARDS.register
 register_norm = NORMS.register
 register_position = POSITIONS.register
 register_block = BLOCKS.register
+register_connection = CONNECTIONS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
 
@@ -295,7 +316,7 @@ def build_part(registry: _Registry, spec: PartSpec, runtime) -> Part:
     return registry.get(spec.kind)(spec.params, prefix=spec.prefix, runtime=runtime)
 
 
-FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}
+FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "connection": CONNECTIONS}
 
 
 def build_layer(spec: LayerSpec, runtime) -> Block:

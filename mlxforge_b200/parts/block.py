@@ -20,3 +20,39 @@ class PreNormBlock(Block):
         x = self.feed_forward_norm.add_forward(residual, d)
         d = self.feed_forward.forward(x, batch)
         return residual, d
+
+
+@register_block("stream_prenorm")
+class StreamPreNormBlock(Block):
+    """Pre-norm over one or several residual streams: each sublayer (the mixer, then the
+    feed-forward if the layer has one) reads the streams through its connection, runs on the norm
+    of what it read, and its result is written back through the same connection.  The connections
+    stand in the roles ``mixer_connection`` and ``feed_forward_connection``; a layer without them
+    has the ordinary residual sum.  The norms must take ``read=`` (``group_rmsnorm`` does).  A
+    mixer whose last projection has a bias may leave it in ``output_bias`` instead of adding it:
+    it then joins the stream write."""
+
+    roles = ("mixer", "mixer_norm")
+
+    def __init__(self, by_role, runtime):
+        super().__init__(by_role, runtime)
+        if self.feed_forward is not None and self.feed_forward_norm is None:
+            raise ValueError("stream_prenorm: a feed-forward needs a feed_forward_norm")
+        self.mixer_connection = self.by_role.get("mixer_connection")
+        self.feed_forward_connection = self.by_role.get("feed_forward_connection")
+
+    @staticmethod
+    def _write(connection, delta, bias=None):
+        from .connections import StreamWrite
+        return connection.write(delta, bias) if connection is not None else StreamWrite(delta, bias)
+
+    def forward(self, residual, pending, batch, cache, writes_cache: bool = True):
+        c = self.mixer_connection
+        x = self.mixer_norm.add_forward(residual, pending, read=c.w_in if c is not None else None)
+        d = self.mixer.forward(x, batch, cache, writes_cache)
+        pending = self._write(c, d, getattr(self.mixer, "output_bias", None))
+        if self.feed_forward is not None:
+            c = self.feed_forward_connection
+            x = self.feed_forward_norm.add_forward(residual, pending, read=c.w_in if c is not None else None)
+            pending = self._write(c, self.feed_forward.forward(x, batch))
+        return residual, pending

@@ -1,0 +1,61 @@
+"""Connections between a sublayer and several residual streams ("hyper-connections").
+
+A model with ``S`` streams keeps ``x_1 .. x_S`` per token, all equal to the embedding's output at
+the start.  A sublayer reads ``u = sum_s in[s] x_s``, runs on ``norm(u)``, and its result ``y`` is
+written back as ``x_t <- sum_s mix[s, t] x_s + out[t] y`` (all ``t`` at once from the old streams;
+``mix`` is indexed ``[from, to]``).  At the end the model's output is the sum of the streams.  With
+``S = 1`` and all three weights 1 this is the ordinary residual sum.
+
+The write-back is not done by the connection: it hands a ``StreamWrite`` on as the layer's pending
+delta, and the norm of the next sublayer (``group_rmsnorm``) applies it in the kernel that also
+reads and normalises, as the single stream's add is fused into the next RMSNorm.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Dict, Optional
+
+import torch
+
+from .base import Connection, TensorSpec, register_connection
+
+
+@dataclass
+class StreamWrite:
+    """A sublayer's result that has not been written into the streams yet: ``delta`` [T, H] (plus
+    ``bias`` [H], 32-bit, if the sublayer's last projection has one that was not added), and the
+    weights of the write (None: identity mixing, out = 1)."""
+
+    delta: Optional[Any]
+    bias: Optional[Any] = None
+    mix: Optional[Any] = None
+    out: Optional[Any] = None
+
+
+@register_connection("hyper")
+class HyperConnection(Connection):
+    graph_safe = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.streams = int(params["streams"])
+        if not (1 <= self.streams <= 8):
+            raise ValueError(f"hyper connection: {self.streams} streams (1 to 8 are supported)")
+        self.w_in = self.w_out = self.w_mix = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        s = self.streams
+        return {self.prefix + "in": TensorSpec((s,), role="vector"),
+                self.prefix + "out": TensorSpec((s,), role="vector"),
+                self.prefix + "mix": TensorSpec((s, s), role="vector")}
+
+    def bind(self, tensors) -> None:
+        self.w_in = tensors[self.prefix + "in"].to(torch.float32).contiguous()
+        self.w_out = tensors[self.prefix + "out"].to(torch.float32).contiguous()
+        self.w_mix = tensors[self.prefix + "mix"].to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return (2 * self.streams + self.streams ** 2) * 4
+
+    def write(self, delta, bias=None) -> StreamWrite:
+        return StreamWrite(delta, bias, self.w_mix, self.w_out)

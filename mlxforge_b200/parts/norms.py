@@ -39,3 +39,48 @@ class RMSNorm(Norm):
             out = self.rt.buffer("norm.out", (n, self.size))
         ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
         return out
+
+
+@register_norm("group_rmsnorm")
+class GroupRMSNorm(Norm):
+    """RMS norm in groups: the channels are cut into ``groups`` equal consecutive parts, each divided
+    by its own ``sqrt(mean(part^2) + eps)``, and the whole is multiplied by the weight (``groups`` = 1
+    is RMSNorm).  It also knows models with several residual streams (``streams``): the stream tensor
+    is then [T, streams * size], a pending ``StreamWrite`` (see ``connections.py``) is written back
+    into the streams first, and the streams are read with the weights ``read`` (None: their plain sum)
+    before the norm; all of it is one kernel."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.groups = int(params.get("groups", 1) or 1)
+        self.streams = int(params.get("streams", 1) or 1)
+        self.name = self.prefix + str(params.get("tensor", "weight"))
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"group_rmsnorm: {self.size} channels do not divide into {self.groups} groups")
+        self.weight = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.name: TensorSpec((self.size,), role="vector")}
+
+    def bind(self, tensors) -> None:
+        self.weight = tensors[self.name].to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.size * 4
+
+    def forward(self, x, out=None):
+        return self.add_forward(x, None, out)
+
+    def add_forward(self, residual, delta, out=None, rows=None, read=None):
+        from .connections import StreamWrite
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        if out is None:
+            out = self.rt.buffer("norm.out", (n, self.size))
+        w = delta if isinstance(delta, StreamWrite) else StreamWrite(delta)
+        ops.hyper_update_norm(residual, w.delta, w.bias, w.mix, w.out, read, self.weight, self.eps, self.groups, out,
+                              self.streams, rows)
+        return out

@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 from ..parts.base import TensorSpec
-from .safetensors_io import SafetensorsFile, model_files
+from .safetensors_io import SafetensorsFile, model_files, read_header
 
 
 class WeightError(ValueError):
@@ -59,6 +59,17 @@ def check_names(specs: Dict[str, TensorSpec], found: Dict[str, tuple], where: st
                    if n in found and tuple(found[n]) != tuple(s.shape))
     if missing or unexpected or wrong:
         raise WeightError(missing, unexpected, wrong, where)
+
+
+def tensor_shapes(model_dir: str) -> Dict[str, tuple]:
+    """Name -> shape of every tensor of the checkpoint, from the files' headers alone."""
+    out: Dict[str, tuple] = {}
+    for p in model_files(model_dir):
+        for e in read_header(p):
+            name = clean_name(e.name)
+            if name is not None:
+                out[name] = tuple(e.shape)
+    return out
 
 
 def _to_torch(a: np.ndarray, tag: str, exact: bool = False) -> torch.Tensor:

@@ -4,7 +4,8 @@
 The reference has no such mode (it always loads a checkpoint,
 src/core/weights.cpp:208-265); its tests need the real Llama-3.2-1B files.  Here
 every matrix is seeded normal with ``std`` (0.02 unless told otherwise) and
-every norm weight is ``1 + N(0, norm_std)`` (exactly 1 when ``norm_std`` is 0).
+every norm weight is ``1 + N(0, norm_std)`` (exactly 1 when ``norm_std`` is 0); an
+architecture may give a tensor a kind of its own, ``(mean, std)`` or ``("eye", std)``.
 Each tensor has its own generator stream keyed by (seed, position in the file),
 so a tensor's values do not depend on the others' sizes.
 """
@@ -54,6 +55,11 @@ def write_random_model(model_dir: str, config: ModelConfig, seed: int, *, dtype:
             a = torch.ones(shape, dtype=torch.float32)
             if norm_std:
                 a += torch.empty(shape, dtype=torch.float32).normal_(0.0, float(norm_std), generator=g)
+        elif isinstance(kind, tuple) and kind[0] == "eye":       # the identity plus noise
+            a = torch.eye(shape[0], shape[1], dtype=torch.float32)
+            a += torch.empty(shape, dtype=torch.float32).normal_(0.0, float(kind[1]), generator=g)
+        elif isinstance(kind, tuple):                            # (mean, std) of a normal draw
+            a = torch.empty(shape, dtype=torch.float32).normal_(float(kind[0]), float(kind[1]), generator=g)
         else:
             a = torch.empty(shape, dtype=torch.float32).normal_(0.0, float(std), generator=g)
         if dtype == "bfloat16":
