@@ -67,6 +67,14 @@ _SIGNATURES = {
     "mf_moe_route": [_P, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P],
     "mf_moe_rows": [_P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float, c_float, _P],
     "mf_moe_combine": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
+    "mf_attention_talking_tc_ok": [c_int, c_int, c_int, c_int, c_int],
+    "mf_attention_talking_tc": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int,
+                                c_int, c_float, c_float, _P, c_int, c_int, _P],
+    "mf_moe_sort": [_P, c_int, c_int, c_int, _P, _P, _P, _P, _P],
+    "mf_moe_grouped_ok": [c_int, c_int, c_int],
+    "mf_moe_grouped_max_tiles": [c_int, c_int, c_int],
+    "mf_moe_grouped_up": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P],
+    "mf_moe_grouped_down": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
 }
 
 MF_ERRORS = {10001: "a size or option this kernel does not take", 10002: "an unsupported dtype"}

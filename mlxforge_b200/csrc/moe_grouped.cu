@@ -1,0 +1,222 @@
+// Experts for many tokens: the (token, choice) pairs are ordered by expert and every expert's
+// pairs go through tensor-core tiles, so an expert's matrices are read once per tile of 64 pairs
+// instead of once per pair.  The formulas are those of moe.cu.
+//
+//   mf_moe_sort     one block: counts per expert, offsets, a row for every pair (slot_of), the
+//                   token of every row (row_token), and the list of tiles (expert, first row, rows).
+//                   Which row a pair gets inside its expert's range is not fixed, and need not be:
+//                   every row is computed by itself, and the sum over a token's experts is taken in
+//                   the order of the choice by the combine kernel.
+//   mf_moe_grouped_up    act[row] = g sigmoid(alpha g) (u + 1) with g, u the clamped gate and up
+//                   products of the row's token (gathered by row_token), bfloat16.
+//   mf_moe_grouped_down  y[row] = Wd_e act[row], 32-bit.
+//
+// Both products are mma.sync m16n8k16 tiles of 64 rows x 64 columns, four warps, K in steps of 32
+// through shared memory.  The launches cover the largest possible number of tiles (known on the
+// host: pairs / 64 + experts); blocks beyond the count the sort kernel wrote return at once, so a
+// step's launches do not depend on its data.
+#include "common.cuh"
+
+#define MG_BM 64
+#define MG_BN 64
+#define MG_BK 32
+#define MG_LD (MG_BK + 8)
+#define MG_MAX_EXPERTS 1024
+
+__device__ __forceinline__ void mg_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// meta: [0] number of tiles; tiles: [max_tiles][3] = expert, first row, rows
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int top, int* __restrict__ slot_of,
+                int* __restrict__ row_token, int* __restrict__ meta, int* __restrict__ tiles) {
+  __shared__ int count[MG_MAX_EXPERTS], offset[MG_MAX_EXPERTS], cursor[MG_MAX_EXPERTS];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = cursor[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0, nt = 0;
+    for (int e = 0; e < E; e++) {
+      offset[e] = off;
+      for (int r = 0; r < count[e]; r += MG_BM) {
+        tiles[3 * nt] = e;
+        tiles[3 * nt + 1] = off + r;
+        tiles[3 * nt + 2] = min(MG_BM, count[e] - r);
+        nt++;
+      }
+      off += count[e];
+    }
+    meta[0] = nt;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = ids[i];
+    const int row = offset[e] + atomicAdd(&cursor[e], 1);
+    slot_of[i] = row;
+    row_token[row] = i / top;
+  }
+}
+
+MF_API int mf_moe_sort(const int* ids, int T, int E, int top, int* slot_of, int* row_token, int* meta, int* tiles,
+                       cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E < 1 || E > MG_MAX_EXPERTS) return MF_ERR_BAD_ARG;
+  mf_count(MF_K_MOE_SORT);
+  moe_sort_kernel<<<1, 1024, 0, stream>>>(ids, T * top, E, top, slot_of, row_token, meta, tiles);
+  return (int)cudaGetLastError();
+}
+
+// One 64 x 64 tile: acc += A[64 rows, K] * B[64 rows of W, K]^T, A rows given by pointers.
+// `arow(r)` -> pointer to row r of A (or null), `brow(n)` -> pointer to row n of W (or null).
+template <int NB, typename ARow, typename BRow>
+__device__ __forceinline__ void mg_tile(float (&acc)[NB][MG_BN / 8][4], int K, ARow arow, BRow brow,
+                                        __nv_bfloat16* As, __nv_bfloat16* Bs) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r0 = lane >> 2, c2 = (lane & 3) * 2;
+  for (int k0 = 0; k0 < K; k0 += MG_BK) {
+    __syncthreads();
+    // 64 rows x 32 columns = 256 pieces of 16 bytes per operand
+    for (int i = tid; i < MG_BM * (MG_BK / 8); i += blockDim.x) {
+      const int r = i / (MG_BK / 8), c = (i - r * (MG_BK / 8)) * 8;
+      const __nv_bfloat16* p = arow(r);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (p && k0 + c < K) v = *reinterpret_cast<const uint4*>(p + k0 + c);
+      *reinterpret_cast<uint4*>(As + r * MG_LD + c) = v;
+    }
+    for (int i = tid; i < NB * MG_BN * (MG_BK / 8); i += blockDim.x) {
+      const int n = i / (MG_BK / 8), c = (i - n * (MG_BK / 8)) * 8;
+      const __nv_bfloat16* p = brow(n);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (p && k0 + c < K) v = *reinterpret_cast<const uint4*>(p + k0 + c);
+      *reinterpret_cast<uint4*>(Bs + n * MG_LD + c) = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MG_BK; kk += 16) {
+      uint32_t af[4];
+      const __nv_bfloat16* ar = As + (warp * 16 + r0) * MG_LD + kk + c2;
+      af[0] = *reinterpret_cast<const uint32_t*>(ar);
+      af[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * MG_LD);
+      af[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
+      af[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * MG_LD + 8);
+#pragma unroll
+      for (int b = 0; b < NB; b++) {
+#pragma unroll
+        for (int nt = 0; nt < MG_BN / 8; nt++) {
+          const __nv_bfloat16* br = Bs + (b * MG_BN + nt * 8 + r0) * MG_LD + kk + c2;
+          mg_mma(acc[b][nt], af, *reinterpret_cast<const uint32_t*>(br), *reinterpret_cast<const uint32_t*>(br + 8));
+        }
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128)
+moe_grouped_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu,
+                      const int* __restrict__ row_token, const int* __restrict__ meta, const int* __restrict__ tiles,
+                      __nv_bfloat16* __restrict__ act, int H, int ff, float limit, float alpha) {
+  __shared__ __align__(16) __nv_bfloat16 As[MG_BM * MG_LD];
+  __shared__ __align__(16) __nv_bfloat16 Bs[2 * MG_BN * MG_LD];
+  if ((int)blockIdx.x >= meta[0]) return;
+  const int e = tiles[3 * blockIdx.x], row_first = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+  const int n0 = blockIdx.y * MG_BN;
+  const __nv_bfloat16* wg = w_gu + (long long)e * 2 * ff * H;
+  const __nv_bfloat16* wu = wg + (long long)ff * H;
+  float acc[2][MG_BN / 8][4];
+#pragma unroll
+  for (int b = 0; b < 2; b++)
+#pragma unroll
+    for (int nt = 0; nt < MG_BN / 8; nt++) acc[b][nt][0] = acc[b][nt][1] = acc[b][nt][2] = acc[b][nt][3] = 0.f;
+  mg_tile<2>(acc, H,
+             [&](int r) { return r < rows ? x + (long long)row_token[row_first + r] * H : nullptr; },
+             [&](int n) {
+               const int col = n0 + (n & (MG_BN - 1));
+               if (col >= ff) return (const __nv_bfloat16*)nullptr;
+               return (n < MG_BN ? wg : wu) + (long long)col * H;
+             },
+             As, Bs);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r0 = warp * 16 + (lane >> 2), c2 = (lane & 3) * 2;
+#pragma unroll
+  for (int nt = 0; nt < MG_BN / 8; nt++) {
+    const int col = n0 + nt * 8 + c2;
+    if (col >= ff) continue;
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+      const int r = r0 + half * 8;
+      if (r >= rows) continue;
+      float v[2];
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        const float g = fminf(acc[0][nt][half * 2 + j], limit);
+        const float u = fminf(fmaxf(acc[1][nt][half * 2 + j], -limit), limit);
+        v[j] = g * (1.0f / (1.0f + __expf(-alpha * g))) * (u + 1.0f);
+      }
+      *reinterpret_cast<__nv_bfloat162*>(act + (long long)(row_first + r) * ff + col) = __floats2bfloat162_rn(v[0], v[1]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128)
+moe_grouped_down_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bfloat16* __restrict__ w_down,
+                        const int* __restrict__ meta, const int* __restrict__ tiles, float* __restrict__ y, int H,
+                        int ff) {
+  __shared__ __align__(16) __nv_bfloat16 As[MG_BM * MG_LD];
+  __shared__ __align__(16) __nv_bfloat16 Bs[MG_BN * MG_LD];
+  if ((int)blockIdx.x >= meta[0]) return;
+  const int e = tiles[3 * blockIdx.x], row_first = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+  const int n0 = blockIdx.y * MG_BN;
+  const __nv_bfloat16* wd = w_down + (long long)e * H * ff;
+  float acc[1][MG_BN / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < MG_BN / 8; nt++) acc[0][nt][0] = acc[0][nt][1] = acc[0][nt][2] = acc[0][nt][3] = 0.f;
+  mg_tile<1>(acc, ff,
+             [&](int r) { return r < rows ? act + (long long)(row_first + r) * ff : nullptr; },
+             [&](int n) { return n0 + n < H ? wd + (long long)(n0 + n) * ff : nullptr; }, As, Bs);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r0 = warp * 16 + (lane >> 2), c2 = (lane & 3) * 2;
+#pragma unroll
+  for (int nt = 0; nt < MG_BN / 8; nt++) {
+    const int col = n0 + nt * 8 + c2;
+    if (col >= H) continue;
+    if (r0 < rows) *reinterpret_cast<float2*>(y + (long long)(row_first + r0) * H + col) = make_float2(acc[0][nt][0], acc[0][nt][1]);
+    if (r0 + 8 < rows)
+      *reinterpret_cast<float2*>(y + (long long)(row_first + r0 + 8) * H + col) = make_float2(acc[0][nt][2], acc[0][nt][3]);
+  }
+}
+
+// the kernels read rows in 16-byte pieces and write pairs of columns
+MF_API int mf_moe_grouped_ok(int H, int ff, int E) {
+  return (H % 8 == 0 && ff % 8 == 0 && E >= 1 && E <= MG_MAX_EXPERTS) ? 1 : 0;
+}
+
+// tiles the launches must cover for T tokens with `top` choices each among E experts
+MF_API int mf_moe_grouped_max_tiles(int T, int top, int E) { return (T * top + MG_BM - 1) / MG_BM + E; }
+
+MF_API int mf_moe_grouped_up(const void* x, const void* w_gu, const int* row_token, const int* meta, const int* tiles,
+                             void* act, int T, int H, int ff, int E, int top, float limit, float alpha,
+                             cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (!mf_moe_grouped_ok(H, ff, E)) return MF_ERR_BAD_ARG;
+  dim3 grid(mf_moe_grouped_max_tiles(T, top, E), (ff + MG_BN - 1) / MG_BN);
+  mf_count(MF_K_MOE_GROUPED);
+  moe_grouped_up_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gu, row_token, meta,
+                                                  tiles, (__nv_bfloat16*)act, H, ff, limit, alpha);
+  return (int)cudaGetLastError();
+}
+
+MF_API int mf_moe_grouped_down(const void* act, const void* w_down, const int* meta, const int* tiles, float* y, int T,
+                               int H, int ff, int E, int top, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (!mf_moe_grouped_ok(H, ff, E)) return MF_ERR_BAD_ARG;
+  dim3 grid(mf_moe_grouped_max_tiles(T, top, E), (H + MG_BN - 1) / MG_BN);
+  mf_count(MF_K_MOE_GROUPED);
+  moe_grouped_down_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, meta, tiles,
+                                                    y, H, ff);
+  return (int)cudaGetLastError();
+}

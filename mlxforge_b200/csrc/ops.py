@@ -492,9 +492,61 @@ def moe_combine(y: torch.Tensor, weights: torch.Tensor, slot_of: Optional[torch.
 
 def attention_talking_tc_ok(n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int) -> bool:
     """Whether the tensor-core kernel for portions of prompts takes these sizes."""
-    return False
+    return bool(library().mf_attention_talking_tc_ok(n_heads, n_kv, dim, vdim, page_size))
 
 
-def moe_grouped_ok(hidden: int, ff: int) -> bool:
+def attention_talking_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                         seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, seq_ctx_len: torch.Tensor,
+                         table_row0: int, max_q_len: int, block_table: torch.Tensor, page_size: int, n_heads: int,
+                         n_kv: int, dim: int, vdim: int, scale: float, softcap: float, talk: Optional[torch.Tensor],
+                         window: int, chunk: int) -> None:
+    """Talking-heads attention of prompt portions, bfloat16, on the tensor cores.  ``q`` / ``out`` are the
+    whole step's rows; the three per-sequence arrays describe the sequences that start at row
+    ``table_row0`` of ``block_table``."""
+    _need_cuda(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, block_table, talk)
+    if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
+        raise KernelError("attention_talking_tc: bfloat16 only")
+    check(library().mf_attention_talking_tc(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+                                            seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_ctx_len.data_ptr(),
+                                            table_row0, seq_q_len.shape[0], max_q_len, n_heads, n_kv, dim, vdim,
+                                            block_table.data_ptr(), block_table.shape[1], page_size, scale, softcap,
+                                            _ptr(talk), window, chunk, _stream()), "attention_talking_tc")
+
+
+def moe_grouped_ok(hidden: int, ff: int, n_experts: int) -> bool:
     """Whether the sorted, tiled expert path takes these sizes."""
-    return False
+    return bool(library().mf_moe_grouped_ok(hidden, ff, n_experts))
+
+
+def moe_grouped_max_tiles(T: int, top: int, n_experts: int) -> int:
+    return int(library().mf_moe_grouped_max_tiles(T, top, n_experts))
+
+
+def moe_sort(ids: torch.Tensor, n_experts: int, slot_of: torch.Tensor, row_token: torch.Tensor, meta: torch.Tensor,
+             tiles: torch.Tensor) -> None:
+    """Order the (token, choice) pairs by expert: ``slot_of`` [T * top] the row of every pair, ``row_token``
+    the token of every row, ``meta[0]`` the number of tiles and ``tiles`` [n, 3] = expert, first row, rows."""
+    _need_cuda(ids, slot_of, row_token, meta, tiles)
+    T, top = ids.shape
+    if tiles.numel() < 3 * moe_grouped_max_tiles(T, top, n_experts):
+        raise KernelError("moe_sort: the tile list is too small")
+    check(library().mf_moe_sort(ids.data_ptr(), T, n_experts, top, slot_of.data_ptr(), row_token.data_ptr(),
+                                meta.data_ptr(), tiles.data_ptr(), _stream()), "moe_sort")
+
+
+def moe_grouped_up(x: torch.Tensor, w_gu: torch.Tensor, row_token: torch.Tensor, meta: torch.Tensor,
+                   tiles: torch.Tensor, act: torch.Tensor, top: int, limit: float, alpha: float) -> None:
+    _need_cuda(x, w_gu, row_token, meta, tiles, act)
+    T, H = x.shape
+    E, _, ff, _ = w_gu.shape
+    check(library().mf_moe_grouped_up(x.data_ptr(), w_gu.data_ptr(), row_token.data_ptr(), meta.data_ptr(),
+                                      tiles.data_ptr(), act.data_ptr(), T, H, ff, E, top, limit, alpha, _stream()),
+          "moe_grouped_up")
+
+
+def moe_grouped_down(act: torch.Tensor, w_down: torch.Tensor, meta: torch.Tensor, tiles: torch.Tensor,
+                     y: torch.Tensor, T: int, top: int) -> None:
+    _need_cuda(act, w_down, meta, tiles, y)
+    E, H, ff = w_down.shape
+    check(library().mf_moe_grouped_down(act.data_ptr(), w_down.data_ptr(), meta.data_ptr(), tiles.data_ptr(),
+                                        y.data_ptr(), T, H, ff, E, top, _stream()), "moe_grouped_down")

@@ -90,10 +90,25 @@ class RoutedExperts(FeedForward):
         ids, weights = self.route(x)
         out = rt.buffer("moe.delta", (T, self.hidden))
         if (x.dtype == torch.bfloat16 and T >= self.grouped_min_tokens
-                and ops.moe_grouped_ok(self.hidden, self.ff)):
-            ops.moe_grouped(rt, x, self.w_gu, self.w_down, ids, weights, out, self.limit, self.alpha)
-            return out
+                and ops.moe_grouped_ok(self.hidden, self.ff, self.n_experts)):
+            return self.forward_grouped(x, ids, weights, out)
         y = rt.buffer("moe.y", (T, self.top, self.hidden), torch.float32)
         ops.moe_rows(x, self.w_gu, self.w_down, ids, y, self.limit, self.alpha)
         ops.moe_combine(y, weights, None, out)
+        return out
+
+    def forward_grouped(self, x, ids, weights, out):
+        """Many tokens: pairs ordered by expert, tensor-core tiles, the weighted sum in the order of the choice."""
+        rt, T = self.rt, x.shape[0]
+        i32, n = torch.int32, T * self.top
+        slot_of = rt.buffer("moe.slot_of", (n,), i32)
+        row_token = rt.buffer("moe.row_token", (n,), i32)
+        meta = rt.buffer("moe.meta", (4,), i32)
+        tiles = rt.buffer("moe.tiles", (3 * ops.moe_grouped_max_tiles(T, self.top, self.n_experts),), i32)
+        ops.moe_sort(ids, self.n_experts, slot_of, row_token, meta, tiles)
+        act = rt.buffer("moe.act", (n, self.ff))
+        ops.moe_grouped_up(x, self.w_gu, row_token, meta, tiles, act, self.top, self.limit, self.alpha)
+        y = rt.buffer("moe.y", (n, self.hidden), torch.float32)
+        ops.moe_grouped_down(act, self.w_down, meta, tiles, y, T, self.top)
+        ops.moe_combine(y, weights, slot_of, out)
         return out
