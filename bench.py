@@ -347,6 +347,233 @@ def run_workload(args) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------- --workload notirax
+# The Notirax design at sizes that resemble a real model's layers, beside the closest existing
+# model (the Llama decoder) at equal size: the same width, heads, head size, layers and
+# vocabulary, and a feed-forward as wide as the experts one token uses.
+NOTIRAX_SIZES = {
+    "s": dict(width=1024, heads=8, kv=2, dim=128, experts=32, top=4, ff=512, groups=4, keep=2, chunk=1024, layers=4,
+              vocab=32768, streams=4, norm_groups=4, rank=64, conv=4),
+    "m": dict(width=2048, heads=16, kv=4, dim=128, experts=64, top=6, ff=768, groups=8, keep=4, chunk=2048, layers=4,
+              vocab=32768, streams=4, norm_groups=4, rank=128, conv=4),
+}
+FP32_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12      # FMA lanes x 2 x the maximum SM clock: no measured figure
+
+
+def notirax_config(z):
+    attn = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
+                                           "scale": z["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": z["chunk"]}}}
+    delta = {"type": "channel_delta", "mixer": {"heads": z["heads"], "kv_heads": z["heads"], "dim": z["dim"],
+                                                "vdim": z["dim"], "conv": z["conv"], "decay_rank": z["rank"],
+                                                "gate_rank": z["rank"]}}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 1.0,
+                      "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    layers = [dict(delta if i % 2 == 0 else attn, mlp=mlp) for i in range(z["layers"])]
+    return {"architecture": "Notirax", "vocab": z["vocab"], "width": z["width"], "streams": z["streams"],
+            "norm": {"eps": 1e-6, "groups": z["norm_groups"]}, "layers": layers}
+
+
+def llama_like(z):
+    return dict(LLAMA_1B, num_hidden_layers=z["layers"], hidden_size=z["width"], num_attention_heads=z["heads"],
+                num_key_value_heads=z["kv"], head_dim=z["dim"], intermediate_size=z["top"] * z["ff"],
+                vocab_size=z["vocab"], rope_scaling=None)
+
+
+class KernelTimes:
+    """Records every call of the named launchers during one step, then times each recorded call
+    alone: an event pair around the launch, the L2 flushed before it, the median of `reps`."""
+
+    def __init__(self, names):
+        from mlxforge_b200.csrc import ops
+        self.ops, self.names, self.calls, self.saved = ops, names, [], {}
+
+    def __enter__(self):
+        for n in self.names:
+            fn = getattr(self.ops, n)
+            self.saved[n] = fn
+
+            def rec(*a, _n=n, _fn=fn, **k):
+                self.calls.append((_n, _fn, a, k))
+                return _fn(*a, **k)
+            setattr(self.ops, n, rec)
+        return self
+
+    def __exit__(self, *exc):
+        for n, fn in self.saved.items():
+            setattr(self.ops, n, fn)
+
+    def measure(self, reps=7):
+        import torch
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        out = {}
+        for n, fn, a, k in self.calls:
+            ts = []
+            for i in range(reps + 2):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn(*a, **k)
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= 2:
+                    ts.append(e0.elapsed_time(e1) * 1e3)
+            out.setdefault(n, []).append((statistics.median(ts), a, k))
+        return out
+
+
+def _nbytes(*ts):
+    return sum(t.numel() * t.element_size() for t in ts if t is not None)
+
+
+def kernel_work(name, a, k, info):
+    """(bytes moved, tensor FLOPs, 32-bit FLOPs) that one call has to do, from its operands."""
+    T, pairs, ctx_keys = info["tokens"], info["pairs"], info["ctx_keys"]
+    if name == "hyper_update_norm":
+        streams, delta, out, rows = a[0], a[1], a[9], (a[11] if len(a) > 11 else k.get("rows"))
+        n = out.shape[0]
+        s_bytes = n * streams.shape[1] * 4
+        return (s_bytes * (2 if delta is not None and rows is None else 1) + _nbytes(out) + (n * out.shape[1] * delta.element_size() if delta is not None else 0), 0, 0)
+    if name == "add_rmsnorm":
+        resid, delta, out = a[0], a[1], a[4]
+        n = out.shape[0]
+        rows = a[5] if len(a) > 5 else k.get("rows")
+        return (n * resid.shape[1] * 4 * (2 if delta is not None and rows is None else 1) + _nbytes(out) + (n * out.shape[1] * delta.element_size() if delta is not None else 0), 0, 0)
+    if name == "attention_talking_tc":
+        H, dim, vdim = a[11], a[13], a[14]
+        return (0, 2.0 * pairs * H * (dim + vdim), 2.0 * pairs * H * H)
+    if name == "attention_prefill":
+        H, hd = a[11], a[13]
+        return (0, 2.0 * pairs * H * 2 * hd, 0)
+    if name == "attention_talking":
+        n_kv, dim, vdim = a[9], a[10], a[11]
+        return (ctx_keys * n_kv * (dim + vdim) * 2, 0, 0)
+    if name == "attention_decode":
+        n_kv, hd = a[11], a[12]
+        return (ctx_keys * n_kv * 2 * hd * 2, 0, 0)
+    if name == "delta_recurrence":
+        qkv, beta, ag, state, o, nh, dim, vdim = a[0], a[1], a[2], a[3], a[5], a[6], a[8], a[9]
+        n_seqs = info["seqs"]
+        return (_nbytes(qkv, beta, o) + ag.shape[0] * nh * dim * 4 + 2 * n_seqs * nh * dim * vdim * 4, 0,
+                7.0 * T * nh * dim * vdim)
+    if name in ("delta_prepare", "delta_gates", "delta_output", "biased_kv_store", "rope_kv_write", "moe_combine",
+                "embed_positions", "embed", "swiglu"):
+        return (_nbytes(*[t for t in a if hasattr(t, "numel") and t.dim() >= 2 and t.numel() < (1 << 28)]), 0, 0)
+    if name == "moe_grouped_up":
+        x, w_gu = a[0], a[1]
+        return (0, 2.0 * T * a[6] * 2 * w_gu.shape[2] * x.shape[1], 0)
+    if name == "moe_grouped_down":
+        w_down = a[1]
+        return (0, 2.0 * a[5] * a[6] * w_down.shape[1] * w_down.shape[2], 0)
+    if name == "moe_rows":
+        x, w_gu, ids = a[0], a[1], a[3]
+        return (ids.numel() * 3 * w_gu.shape[2] * x.shape[1] * 2, 0, 0)
+    if name in ("gemm_bf16", "stream_linear"):
+        x, w, out = a[0], a[1], a[2]
+        return (_nbytes(x, w, out), 2.0 * x.shape[0] * w.shape[0] * w.shape[1], 0)
+    return (0, 0, 0)
+
+
+NOTIRAX_KERNELS = ("embed_positions", "hyper_update_norm", "biased_kv_store", "attention_talking", "attention_talking_tc",
+                   "delta_prepare", "delta_gates", "delta_recurrence", "delta_output", "moe_route", "moe_rows",
+                   "moe_combine", "moe_sort", "moe_grouped_up", "moe_grouped_down", "stream_linear", "gemm_bf16")
+LLAMA_KERNELS = ("embed", "add_rmsnorm", "rope_kv_write", "attention_prefill", "attention_decode", "swiglu",
+                 "stream_linear", "gemm_bf16")
+
+
+def kernel_table(engine, names, tokens, batch, ctx, chunk, pk):
+    """Per kind of kernel: microseconds per call in a prefill of `tokens` tokens and in a decode step of
+    `batch` sequences at `ctx`, and the fraction of the roofline (the slowest of bytes / HBM copy,
+    tensor FLOPs / the library's bfloat16 product and 32-bit FLOPs / the nominal FMA rate)."""
+    import numpy as np
+    import torch
+    from mlxforge_b200.engine.step import StepEntry
+    runner, cache = engine.runner, engine.cache
+    rng = np.random.default_rng(5)
+    vocab = engine.model.spec.vocab_size
+    table = {}
+
+    def visible(n, first=0):
+        return sum((p % chunk if chunk else p) + 1 for p in range(first, first + n))
+
+    def collect(phase, entries, info):
+        with KernelTimes(names) as kt:
+            runner.step(entries)
+            torch.cuda.synchronize()
+        for n, calls in kt.measure().items():
+            us = statistics.median(c[0] for c in calls)
+            b, tf, ff = kernel_work(n, calls[0][1], calls[0][2], info)
+            roof = max(b / (pk["hbm_gbs"] * 1e9), tf / (pk["bf16_tflops"] * 1e12), ff / (FP32_TFLOPS_NOMINAL * 1e12)) * 1e6
+            table[f"{phase}.{n}"] = {"us": round(us, 1), "calls": len(calls), "roof_us": round(roof, 2),
+                                     "frac": round(roof / us, 3) if roof else None,
+                                     "bound": None if not roof else ("hbm" if roof == b / (pk["hbm_gbs"] * 1e9) * 1e6 else
+                                                                     "tensor" if roof == tf / (pk["bf16_tflops"] * 1e12) * 1e6 else "fp32")}
+
+    s = cache.open_sequence()
+    collect("prefill", [StepEntry(s, rng.integers(0, vocab, size=tokens).tolist(), [tokens - 1])],
+            {"tokens": tokens, "pairs": visible(tokens), "ctx_keys": 0, "seqs": 1})
+    cache.close(s)
+    seqs = [cache.open_sequence() for _ in range(batch)]
+    for q in seqs:
+        cache.reserve([(q, ctx - 1)])
+        cache.commit(q, ctx - 1)
+    engine.runner.cuda_graphs, graphs = False, engine.runner.cuda_graphs
+    try:
+        collect("decode", [StepEntry(q, [int(rng.integers(0, vocab))], [0]) for q in seqs],
+                {"tokens": batch, "pairs": 0, "ctx_keys": batch * visible(1, ctx - 1), "seqs": batch})
+    finally:
+        engine.runner.cuda_graphs = graphs
+    for q in seqs:
+        cache.close(q)
+    return table
+
+
+def run_notirax(args) -> int:
+    import torch
+    import mlxforge_b200 as mf
+    from mlxforge_b200.config import config_from_json
+    from mlxforge_b200.csrc import ops
+    pk = peaks()
+    out = {"workload": "notirax", "dtype": "bf16", "peaks": pk,
+           "data": "synthetic: seeded random weights, seeded uniform token ids, random cache contents",
+           "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1), "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for key in ([args.size] if args.size else sorted(NOTIRAX_SIZES)):
+        z = NOTIRAX_SIZES[key]
+        res = {"size": z}
+        for which, cfg_json, names in (("notirax", notirax_config(z), NOTIRAX_KERNELS),
+                                       ("llama_equal_size", llama_like(z), LLAMA_KERNELS)):
+            tmp = tempfile.mkdtemp(prefix="mlxforge_bench_")
+            try:
+                d = mf.write_random_model(os.path.join(tmp, "model"), config_from_json(cfg_json), seed=0, dtype="bfloat16")
+                engine = mf.Engine(model_spec=d, dtype="bfloat16", kv_pool_tokens=(args.batch + 2) * (z["chunk"] + 2048 + 64),
+                                   max_running=max(8, args.batch), token_budget=8192, prefill_chunk=2048)
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            for pool in engine.cache._k + engine.cache._v:
+                pool.normal_(0.0, 1.0)
+            ctx = z["chunk"]
+            t_pre = prefill_device(engine, PREFILL_TOKENS, runs=3, warmup=3)
+            sec, launches, _, _ = decode_device(engine, args.batch, ctx, args.steps, args.warmup)
+            r = {"prefill_tokens": PREFILL_TOKENS, "prefill_ms": round(t_pre * 1e3, 3),
+                 "prefill_tokens_per_s": round(PREFILL_TOKENS / t_pre, 1), "decode_batch": args.batch, "decode_context": ctx,
+                 "decode_ms_per_step": round(sec * 1e3, 4), "decode_tokens_per_s": round(args.batch / sec, 1),
+                 "decode_launches_per_step": launches, "graph_replays": engine.runner.graph_replays,
+                 "weight_bytes_per_step": engine.model.weight_bytes()}
+            if not args.skip_points:
+                r["kernels"] = kernel_table(engine, names, PREFILL_TOKENS, args.batch, ctx,
+                                            z["chunk"] if which == "notirax" else 0, pk)
+            ops.check_kernel_status()
+            res[which] = r
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][key] = res
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 # Kinds of launches that `--without` leaves out of a decode step, to see what each costs inside it.
 LEFT_OUT = ("norms", "rotation", "attention", "qkv", "o", "gate_up", "down", "head", "products")
 
@@ -401,8 +628,10 @@ def main() -> int:
     ap.add_argument("--without", default=None, choices=sorted(LEFT_OUT),
                     help="with --only decode: time the step with the launches of one kind left out (its results are "
                          "wrong; the difference to the full step is what that kind costs inside the step)")
-    ap.add_argument("--workload", default="headline", choices=["headline", "serving", "longctx"],
-                    help="serving: 64 requests on the 3B shape; longctx: 8 x 16,384 tokens on the 8B shape")
+    ap.add_argument("--workload", default="headline", choices=["headline", "serving", "longctx", "notirax"],
+                    help="serving: 64 requests on the 3B shape; longctx: 8 x 16,384 tokens on the 8B shape; notirax: "
+                         "prefill and decode of the Notirax design beside the Llama decoder at equal size, per kernel")
+    ap.add_argument("--size", default=None, choices=sorted(NOTIRAX_SIZES), help="with --workload notirax: one size only")
     args = ap.parse_args()
     args.shape_given = args.shape is not None
     args.shape = args.shape or "1b"
@@ -414,6 +643,8 @@ def main() -> int:
         print(json.dumps({"unavailable": f"this engine runs on one GPU; --gpus {args.gpus} is not supported"}))
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.workload == "notirax":
+        return run_notirax(args)
     if args.workload != "headline":
         return run_workload(args)
 

@@ -12,6 +12,15 @@
 //   3. warp h:  online softmax of its mixed scores (32-bit), P_h rounded to bfloat16 as the
 //               A operand, O_h += P_h V_g(h).
 //
+// Keys and values of a tile come in by cp.async (16 bytes a copy) after the two pages of the
+// tile's granules have been looked up once, so a tile waits for one round trip to memory and
+// not for one per piece.
+//
+// Decoding (one query per sequence) runs the same kernel with the keys cut into splits of
+// TT_SPLIT_TILES tiles that start at multiples of that many tiles: a block per (sequence, split)
+// writes its unnormalised output with its running maximum and sum, and a merge kernel joins the
+// splits.  A split's range depends on positions only.
+//
 // Steps 1 and 3 are tensor-core work of 2 * 16 * 32 * (dim + vdim) MACs per head; step 2 is
 // H^2 * 512 32-bit FMAs per tile plus a tanh and an exponential per score, which is what bounds
 // the kernel: the mixing has to stay 32-bit.
@@ -20,6 +29,7 @@
 #define TT_BM 16
 #define TT_BN 32
 #define TT_SPAD 4          // floats of padding per row of the score tile
+#define TT_SPLIT_TILES 4   // key tiles per split when decoding (128 keys)
 
 __device__ __forceinline__ void tt_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -30,6 +40,13 @@ __device__ __forceinline__ void tt_mma(float (&c)[4], const uint32_t (&a)[4], ui
 __device__ __forceinline__ void tt_ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* p) {
   const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void tt_cp_async16(void* smem, const void* gmem) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(addr), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void tt_cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }
 __device__ __forceinline__ uint32_t tt_pack(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -54,6 +71,9 @@ struct TtArgs {
   int table_row0, bt_stride, page_size, n_heads, n_kv, dim;
   float scale, softcap;
   int window, chunk;
+  int splits;               // 0: every block walks all its keys; else gridDim.z splits of TT_SPLIT_TILES tiles
+  float* part_o;            // [rows, splits, H, VDIM] unnormalised outputs of the splits
+  float* part_ml;           // [rows, splits, H, 2]    running maximum and sum
 };
 
 template <int VDIM, int MAXH>
@@ -106,33 +126,45 @@ talking_attention_tc_kernel(const TtArgs a) {
   const int g_own = warp / rep;
   const bool has_head = warp < H;
 
-  for (int k0 = (lo0 / TT_BN) * TT_BN; k0 <= pos_last; k0 += TT_BN) {
+  int k_first = (lo0 / TT_BN) * TT_BN, k_last = pos_last;
+  if (a.splits > 0) {      // this block's share: tiles [z, z + 1) * TT_SPLIT_TILES of the sequence
+    const int span = TT_SPLIT_TILES * TT_BN;
+    const int first_split = k_first / span;
+    k_first = max(k_first, (first_split + (int)blockIdx.z) * span);
+    k_last = min(k_last, (first_split + (int)blockIdx.z + 1) * span - 1);
+  }
+  for (int k0 = k_first; k0 <= k_last; k0 += TT_BN) {
     __syncthreads();       // the tile before is done with Ks, Vs and sc (and Qs, tk are written)
     // keys and values of the tile: two granules of 16 positions, each inside one page
+    long long pg[TT_BN / 16];
+#pragma unroll
+    for (int gq = 0; gq < TT_BN / 16; gq++) {
+      const int p0 = k0 + 16 * gq;
+      pg[gq] = (p0 <= pos_last && p0 + 15 >= lo0) ? (long long)table[p0 / a.page_size] : -1;
+    }
     for (int i = tid; i < G * TT_BN * dv8; i += nthreads) {
-      const int g = i / (TT_BN * dv8), rem = i - g * TT_BN * dv8;
-      const int j = rem / dv8, c = (rem - j * dv8) * 8;
+      const int row = i / dv8, c = (i - row * dv8) * 8;
+      const int g = row / TT_BN, j = row - g * TT_BN;
       const int pj = k0 + j;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (pj >= lo0 && pj <= pos_last) {
-        const int blk = pj / a.page_size, slot = pj - blk * a.page_size;
-        const long long page = table[blk];
-        v = *reinterpret_cast<const uint4*>(a.k_pool + ((page * G + g) * a.page_size + slot) * dim + c);
-      }
-      *reinterpret_cast<uint4*>(Ks + ((size_t)g * TT_BN + j) * qs_ld + c) = v;
+      __nv_bfloat16* dst = Ks + (size_t)row * qs_ld + c;
+      const long long page = (j >> 4) ? pg[1] : pg[0];
+      if (pj >= lo0 && pj <= pos_last && page >= 0)
+        tt_cp_async16(dst, a.k_pool + ((page * G + g) * a.page_size + (pj % a.page_size)) * dim + c);
+      else
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
     for (int i = tid; i < G * TT_BN * (VDIM / 8); i += nthreads) {
-      const int g = i / (TT_BN * (VDIM / 8)), rem = i - g * TT_BN * (VDIM / 8);
-      const int j = rem / (VDIM / 8), c = (rem - j * (VDIM / 8)) * 8;
+      const int row = i / (VDIM / 8), c = (i - row * (VDIM / 8)) * 8;
+      const int g = row / TT_BN, j = row - g * TT_BN;
       const int pj = k0 + j;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (pj >= lo0 && pj <= pos_last) {
-        const int blk = pj / a.page_size, slot = pj - blk * a.page_size;
-        const long long page = table[blk];
-        v = *reinterpret_cast<const uint4*>(a.v_pool + ((page * G + g) * a.page_size + slot) * VDIM + c);
-      }
-      *reinterpret_cast<uint4*>(Vs + ((size_t)g * TT_BN + j) * vs_ld + c) = v;
+      __nv_bfloat16* dst = Vs + (size_t)row * vs_ld + c;
+      const long long page = (j >> 4) ? pg[1] : pg[0];
+      if (pj >= lo0 && pj <= pos_last && page >= 0)
+        tt_cp_async16(dst, a.v_pool + ((page * G + g) * a.page_size + (pj % a.page_size)) * VDIM + c);
+      else
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
+    tt_cp_async_wait_all();
     __syncthreads();
 
     // 1. raw scores of this warp's head
@@ -169,23 +201,21 @@ talking_attention_tc_kernel(const TtArgs a) {
     }
     __syncthreads();
 
-    // 2. the heads mixed and the mask, four keys of one query per thread and pass
-    for (int quad = tid; quad < TT_BM * (TT_BN / 4); quad += nthreads) {
-      const int r = quad / (TT_BN / 4), j4 = (quad - r * (TT_BN / 4)) * 4;
-      float acc[MAXH][4];
+    // 2. the heads mixed and the mask, two keys of one query per thread and pass
+    for (int pair = tid; pair < rows * (TT_BN / 2); pair += nthreads) {
+      const int r = pair / (TT_BN / 2), j2 = (pair - r * (TT_BN / 2)) * 2;
+      float acc[MAXH][2];
 #pragma unroll
-      for (int h = 0; h < MAXH; h++) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
+      for (int h = 0; h < MAXH; h++) acc[h][0] = acc[h][1] = 0.f;
       if (a.talk) {
         for (int g = 0; g < H; g++) {
-          const float4 sg = *reinterpret_cast<const float4*>(sc + ((size_t)g * TT_BM + r) * sc_ld + j4);
+          const float2 sg = *reinterpret_cast<const float2*>(sc + ((size_t)g * TT_BM + r) * sc_ld + j2);
 #pragma unroll
           for (int h = 0; h < MAXH; h++) {
             if (h < H) {
               const float t = tk[h * H + g];
               acc[h][0] = fmaf(t, sg.x, acc[h][0]);
               acc[h][1] = fmaf(t, sg.y, acc[h][1]);
-              acc[h][2] = fmaf(t, sg.z, acc[h][2]);
-              acc[h][3] = fmaf(t, sg.w, acc[h][3]);
             }
           }
         }
@@ -193,8 +223,8 @@ talking_attention_tc_kernel(const TtArgs a) {
 #pragma unroll
         for (int h = 0; h < MAXH; h++) {
           if (h < H) {
-            const float4 sg = *reinterpret_cast<const float4*>(sc + ((size_t)h * TT_BM + r) * sc_ld + j4);
-            acc[h][0] = sg.x; acc[h][1] = sg.y; acc[h][2] = sg.z; acc[h][3] = sg.w;
+            const float2 sg = *reinterpret_cast<const float2*>(sc + ((size_t)h * TT_BM + r) * sc_ld + j2);
+            acc[h][0] = sg.x; acc[h][1] = sg.y;
           }
         }
       }
@@ -202,18 +232,13 @@ talking_attention_tc_kernel(const TtArgs a) {
       int lo = 0;
       if (a.window > 0) lo = max(lo, pi - a.window + 1);
       if (a.chunk > 0) lo = max(lo, pi / a.chunk * a.chunk);
-      bool ok[4];
-#pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const int pj = k0 + j4 + e;
-        ok[e] = r < rows && pj >= lo && pj <= pi;
-      }
+      const int pj = k0 + j2;
+      const bool ok0 = pj >= lo && pj <= pi, ok1 = pj + 1 >= lo && pj + 1 <= pi;
 #pragma unroll
       for (int h = 0; h < MAXH; h++) {
         if (h < H)
-          *reinterpret_cast<float4*>(sc + ((size_t)h * TT_BM + r) * sc_ld + j4) =
-              make_float4(ok[0] ? acc[h][0] : -INFINITY, ok[1] ? acc[h][1] : -INFINITY,
-                          ok[2] ? acc[h][2] : -INFINITY, ok[3] ? acc[h][3] : -INFINITY);
+          *reinterpret_cast<float2*>(sc + ((size_t)h * TT_BM + r) * sc_ld + j2) =
+              make_float2(ok0 ? acc[h][0] : -INFINITY, ok1 ? acc[h][1] : -INFINITY);
       }
     }
     __syncthreads();
@@ -225,8 +250,10 @@ talking_attention_tc_kernel(const TtArgs a) {
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
       for (int nt = 0; nt < TT_BN / 8; nt++) {
-        const float2 x = *reinterpret_cast<const float2*>(sh + (size_t)r0 * sc_ld + nt * 8 + c2);
-        const float2 y = *reinterpret_cast<const float2*>(sh + (size_t)(r0 + 8) * sc_ld + nt * 8 + c2);
+        float2 x = *reinterpret_cast<const float2*>(sh + (size_t)r0 * sc_ld + nt * 8 + c2);
+        float2 y = *reinterpret_cast<const float2*>(sh + (size_t)(r0 + 8) * sc_ld + nt * 8 + c2);
+        if (r0 >= rows) x = make_float2(-INFINITY, -INFINITY);          // rows beyond the portion were not mixed
+        if (r0 + 8 >= rows) y = make_float2(-INFINITY, -INFINITY);
         s[nt][0] = x.x; s[nt][1] = x.y; s[nt][2] = y.x; s[nt][3] = y.y;
         mx[0] = fmaxf(mx[0], fmaxf(x.x, x.y));
         mx[1] = fmaxf(mx[1], fmaxf(y.x, y.y));
@@ -282,6 +309,19 @@ talking_attention_tc_kernel(const TtArgs a) {
       l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 1);
       l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 2);
     }
+    if (a.splits > 0) {      // one query per sequence: row 0, held by the first four lanes
+      if (r0 == 0) {
+        const long long slot = ((long long)(q_start + row0) * a.splits + blockIdx.z) * H + warp;
+#pragma unroll
+        for (int nt = 0; nt < VDIM / 8; nt++)
+          *reinterpret_cast<float2*>(a.part_o + slot * VDIM + nt * 8 + c2) = make_float2(o[nt][0], o[nt][1]);
+        if (c2 == 0) {
+          a.part_ml[slot * 2] = m_run[0];
+          a.part_ml[slot * 2 + 1] = l_run[0];
+        }
+      }
+      return;
+    }
     const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
 #pragma unroll
     for (int nt = 0; nt < VDIM / 8; nt++) {
@@ -309,6 +349,30 @@ MF_API int mf_attention_talking_tc_ok(int n_heads, int n_kv, int dim, int vdim, 
   return tt_smem_bytes(n_heads, n_kv, dim, vdim) <= 200 * 1024 ? 1 : 0;
 }
 
+// out[t, h] = sum_z o_z e^{m_z - m} / sum_z l_z e^{m_z - m}, the splits in their order
+__global__ void __launch_bounds__(128)
+talking_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                               __nv_bfloat16* __restrict__ out, int splits, int H, int vdim) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* ml = part_ml + ((long long)t * splits * H + h) * 2;
+  float m = -INFINITY;
+  for (int z = 0; z < splits; z++) m = fmaxf(m, ml[(long long)z * H * 2]);
+  float l = 0.f;
+  for (int z = 0; z < splits; z++) {
+    const float mz = ml[(long long)z * H * 2];
+    if (mz != -INFINITY) l += ml[(long long)z * H * 2 + 1] * __expf(mz - m);
+  }
+  const float inv = 1.0f / l;
+  for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < splits; z++) {
+      const float mz = ml[(long long)z * H * 2];
+      if (mz != -INFINITY) acc += part_o[(((long long)t * splits + z) * H + h) * vdim + c] * __expf(mz - m);
+    }
+    out[((long long)t * H + h) * vdim + c] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
 template <int VDIM, int MAXH>
 static int tt_launch(const TtArgs& a, int n_seqs, int max_q_len, cudaStream_t stream) {
   const size_t smem = tt_smem_bytes(a.n_heads, a.n_kv, a.dim, VDIM);
@@ -321,7 +385,7 @@ static int tt_launch(const TtArgs& a, int n_seqs, int max_q_len, cudaStream_t st
     if (e != cudaSuccess) return (int)e;
     once.done[d] = true;
   }
-  dim3 grid((max_q_len + TT_BM - 1) / TT_BM, n_seqs);
+  dim3 grid((max_q_len + TT_BM - 1) / TT_BM, n_seqs, a.splits > 0 ? a.splits : 1);
   const int warps = a.n_heads < 4 ? 4 : a.n_heads;       // at least four warps for the loads and the mixing
   talking_attention_tc_kernel<VDIM, MAXH><<<grid, 32 * warps, smem, stream>>>(a);
   return (int)cudaGetLastError();
@@ -338,7 +402,7 @@ MF_API int mf_attention_talking_tc(const void* q, const void* k_pool, const void
   if (!mf_attention_talking_tc_ok(n_heads, n_kv, dim, vdim, page_size) || n_seqs > 65535) return MF_ERR_BAD_ARG;
   TtArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out,
            seq_q_start, seq_q_len, seq_ctx_len, block_table, talk, table_row0, bt_stride, page_size, n_heads, n_kv, dim,
-           scale, softcap, window, chunk};
+           scale, softcap, window, chunk, 0, nullptr, nullptr};
   mf_count(MF_K_ATTN_TALKING_TC);
 #define TT_CASE(VD)                                                              \
   if (vdim == VD) {                                                              \
@@ -351,4 +415,40 @@ MF_API int mf_attention_talking_tc(const void* q, const void* k_pool, const void
   TT_CASE(128)
 #undef TT_CASE
   return MF_ERR_BAD_ARG;
+}
+
+// Splits that a decode launch needs when no query sees more than `max_keys` keys.
+MF_API int mf_attention_talking_splits(int max_keys) {
+  const int tiles = (max_keys + TT_BN - 1) / TT_BN + 1;       // a range of keys may straddle one tile more
+  return (tiles + TT_SPLIT_TILES - 1) / TT_SPLIT_TILES + 1;   // and one split more
+}
+
+// One query per sequence (the newest token of each), keys cut into splits; q and out hold the
+// n_seqs tokens, row t the token of row t of the block table.  part_o needs
+// n_seqs * splits * n_heads * vdim floats, part_ml n_seqs * splits * n_heads * 2.
+MF_API int mf_attention_talking_decode(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                       const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len, int n_seqs,
+                                       int n_heads, int n_kv, int dim, int vdim, const int* block_table, int bt_stride,
+                                       int page_size, float scale, float softcap, const float* talk, int window,
+                                       int chunk, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (!mf_attention_talking_tc_ok(n_heads, n_kv, dim, vdim, page_size) || n_seqs > 65535 || splits < 1 || splits > 65535)
+    return MF_ERR_BAD_ARG;
+  TtArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out,
+           seq_q_start, seq_q_len, seq_ctx_len, block_table, talk, 0, bt_stride, page_size, n_heads, n_kv, dim,
+           scale, softcap, window, chunk, splits, part_o, part_ml};
+  mf_count(MF_K_ATTN_TALKING_TC);
+  int rc = MF_ERR_BAD_ARG;
+#define TT_CASE(VD)                                                         \
+  if (vdim == VD) rc = n_heads <= 8 ? tt_launch<VD, 8>(a, n_seqs, 1, stream) : tt_launch<VD, 16>(a, n_seqs, 1, stream);
+  TT_CASE(32)
+  TT_CASE(64)
+  TT_CASE(96)
+  TT_CASE(128)
+#undef TT_CASE
+  if (rc != 0) return rc;
+  mf_count(MF_K_ATTN_TALKING_MERGE);
+  talking_attention_merge_kernel<<<dim3(n_seqs, n_heads), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, splits,
+                                                                         n_heads, vdim);
+  return (int)cudaGetLastError();
 }

@@ -144,6 +144,7 @@ enum MfKernel {
   MF_K_KV_STORE,              // projection biases and the cache write (key and value sizes may differ)
   MF_K_ATTN_TALKING,          // attention with heads mixed before the softmax, a block per token
   MF_K_ATTN_TALKING_TC,       // the same on tensor cores, a block per tile of queries
+  MF_K_ATTN_TALKING_MERGE,    // joins the key splits of a decode launch of that kernel
   MF_K_DELTA_PREPARE,         // short convolutions, SiLU, unit norms of the delta rule's operands
   MF_K_DELTA_GATES,
   MF_K_DELTA_RECURRENCE,

@@ -173,6 +173,135 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
   }
 }
 
+// The same recurrence with the operands of the coming tokens brought into shared memory ahead of
+// time: stages of DR_CHUNK tokens (q, k and g rows of the head, the block's 16 values, beta) are
+// copied by cp.async into a ring of DR_STAGES, so the serial loop over the tokens reads shared
+// memory only and a token no longer waits for a round trip to memory.  Channel d of a column
+// belongs to lane ((d / 4) % 8) of its eight lanes, so that the eight lanes read 128 consecutive
+// bytes of a row at once.  Needs dim, vdim and the row lengths to be multiples of 4 (16-byte copies).
+#define DR_CHUNK 8
+#define DR_STAGES 4
+
+__device__ __forceinline__ void dr_cp16(void* smem, const void* gmem) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(addr), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void dr_cp4(void* smem, const void* gmem) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(addr), "l"(gmem) : "memory");
+}
+
+template <int DPT>
+__global__ void __launch_bounds__(DR_THREADS)
+delta_recurrence_staged_kernel(const float* __restrict__ qkv, const float* __restrict__ beta,
+                               const float* __restrict__ ag, int ag_ld, float* __restrict__ state,
+                               long long state_stride, const int* __restrict__ seq_q_start,
+                               const int* __restrict__ seq_q_len, const int* __restrict__ slots,
+                               float* __restrict__ o_out, int n_heads, int n_kv, int dim, int vdim) {
+  constexpr int DP = DPT * DR_LANES;                         // channels, padded
+  constexpr int TOK = 3 * DP + DR_COLS + 4;                  // floats of one token in a stage: q, k, g, v, beta
+  extern __shared__ __align__(16) float dr_sm[];             // [DR_STAGES][DR_CHUNK][TOK]
+  const int seq = blockIdx.x, h = blockIdx.y;
+  const int col0 = blockIdx.z * DR_COLS;
+  const int ci = threadIdx.x / DR_LANES, part = threadIdx.x % DR_LANES;
+  const int col = col0 + ci;
+  const int kvh = h / (n_heads / n_kv);
+  const int C = 2 * n_kv * dim + n_heads * vdim;
+  const int start = seq_q_start[seq], n = seq_q_len[seq];
+  const bool live = col < vdim;
+  // the padding of q, k, g and v is never copied: zero once, where there is any
+  if (dim < DP || col0 + DR_COLS > vdim) {
+    for (int i = threadIdx.x; i < DR_STAGES * DR_CHUNK * TOK; i += DR_THREADS) dr_sm[i] = 0.f;
+    __syncthreads();
+  }
+  float* S = state + (long long)slots[seq] * state_stride + (long long)h * dim * vdim;
+  float s[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; i++) {
+    const int d = ((i >> 2) * DR_LANES + part) * 4 + (i & 3);
+    s[i] = (live && d < dim) ? S[(long long)d * vdim + col] : 0.f;
+  }
+  const int d4 = dim / 4;
+  const int n_chunks = (n + DR_CHUNK - 1) / DR_CHUNK;
+  auto issue = [&](int chunk) {
+    if (chunk < n_chunks) {
+      float* st = dr_sm + (size_t)(chunk % DR_STAGES) * DR_CHUNK * TOK;
+      const int t0 = start + chunk * DR_CHUNK, nt = min(DR_CHUNK, n - chunk * DR_CHUNK);
+      for (int i = threadIdx.x; i < nt * 3 * d4; i += DR_THREADS) {
+        const int tok = i / (3 * d4), rem = i - tok * 3 * d4;
+        const int which = rem / d4, c = (rem - which * d4) * 4;
+        const long long t = t0 + tok;
+        const float* src = which == 0 ? qkv + t * C + kvh * dim + c
+                         : which == 1 ? qkv + t * C + (n_kv + kvh) * dim + c
+                                      : ag + t * ag_ld + h * dim + c;
+        dr_cp16(st + tok * TOK + which * DP + c, src);
+      }
+      for (int i = threadIdx.x; i < nt * (DR_COLS / 4); i += DR_THREADS) {
+        const int tok = i / (DR_COLS / 4), c = (i - tok * (DR_COLS / 4)) * 4;
+        if (col0 + c < vdim)
+          dr_cp16(st + tok * TOK + 3 * DP + c, qkv + (long long)(t0 + tok) * C + 2 * n_kv * dim + h * vdim + col0 + c);
+      }
+      for (int tok = threadIdx.x; tok < nt; tok += DR_THREADS)
+        dr_cp4(st + tok * TOK + 3 * DP + DR_COLS, beta + (long long)(t0 + tok) * n_heads + h);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+#pragma unroll
+  for (int c = 0; c < DR_STAGES - 1; c++) issue(c);
+  for (int chunk = 0; chunk < n_chunks; chunk++) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(DR_STAGES - 2) : "memory");
+    __syncthreads();                         // the stage has landed for all, and the stage read before is free
+    issue(chunk + DR_STAGES - 1);
+    const float* st = dr_sm + (size_t)(chunk % DR_STAGES) * DR_CHUNK * TOK;
+    const int nt = min(DR_CHUNK, n - chunk * DR_CHUNK);
+    for (int tok = 0; tok < nt; tok++) {
+      const float* row = st + tok * TOK;
+      const float4* q4 = reinterpret_cast<const float4*>(row);
+      const float4* k4 = reinterpret_cast<const float4*>(row + DP);
+      const float4* g4 = reinterpret_cast<const float4*>(row + 2 * DP);
+      const float v = row[3 * DP + ci], b = row[3 * DP + DR_COLS];
+      float dot0 = 0.f, dot1 = 0.f;
+#pragma unroll
+      for (int i4 = 0; i4 < DPT / 4; i4++) {
+        const float4 g = g4[i4 * DR_LANES + part], k = k4[i4 * DR_LANES + part];
+        s[4 * i4] *= g.x; s[4 * i4 + 1] *= g.y; s[4 * i4 + 2] *= g.z; s[4 * i4 + 3] *= g.w;
+        dot0 = fmaf(s[4 * i4], k.x, dot0);
+        dot1 = fmaf(s[4 * i4 + 1], k.y, dot1);
+        dot0 = fmaf(s[4 * i4 + 2], k.z, dot0);
+        dot1 = fmaf(s[4 * i4 + 3], k.w, dot1);
+      }
+      float dot = dot0 + dot1;
+#pragma unroll
+      for (int off = 1; off < DR_LANES; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+      const float u = b * (v - dot);
+      float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+      for (int i4 = 0; i4 < DPT / 4; i4++) {
+        const float4 k = k4[i4 * DR_LANES + part], q = q4[i4 * DR_LANES + part];
+        s[4 * i4] = fmaf(k.x, u, s[4 * i4]);
+        s[4 * i4 + 1] = fmaf(k.y, u, s[4 * i4 + 1]);
+        s[4 * i4 + 2] = fmaf(k.z, u, s[4 * i4 + 2]);
+        s[4 * i4 + 3] = fmaf(k.w, u, s[4 * i4 + 3]);
+        o0 = fmaf(s[4 * i4], q.x, o0);
+        o1 = fmaf(s[4 * i4 + 1], q.y, o1);
+        o0 = fmaf(s[4 * i4 + 2], q.z, o0);
+        o1 = fmaf(s[4 * i4 + 3], q.w, o1);
+      }
+      float o = o0 + o1;
+#pragma unroll
+      for (int off = 1; off < DR_LANES; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      if (live && part == 0)
+        o_out[(long long)(start + chunk * DR_CHUNK + tok) * n_heads * vdim + h * vdim + col] = o;
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < DPT; i++) {
+    const int d = ((i >> 2) * DR_LANES + part) * 4 + (i & 3);
+    if (live && d < dim) S[(long long)d * vdim + col] = s[i];
+  }
+}
+
 // ------------------------------------------------------------------ read-out norm and gate
 // out[t, h, c] = o[t, h, c] / sqrt(mean_c o^2 + eps) * w[c] * gate[t, h, c]; a warp per (token, head).
 template <typename TO>
@@ -252,6 +381,32 @@ MF_API int mf_delta_recurrence(const float* qkv, const float* beta, const float*
                                                                 seq_q_start, seq_q_len, slots, o_out, n_heads, n_kv, \
                                                                 dim, vdim)
   const int per = (dim + DR_LANES - 1) / DR_LANES;
+  const bool aligned = dim % 4 == 0 && vdim % 4 == 0 && ag_ld % 4 == 0 && ((uintptr_t)qkv & 15) == 0 &&
+                       ((uintptr_t)ag & 15) == 0;
+  if (aligned) {
+    // the staged kernel: operands through a cp.async ring in shared memory
+#define DS_LAUNCH(DPT)                                                                                             \
+  do {                                                                                                             \
+    const size_t smem = (size_t)DR_STAGES * DR_CHUNK * (3 * DPT * DR_LANES + DR_COLS + 4) * sizeof(float);         \
+    static DeviceOnce once;                                                                                        \
+    const int dev = mf_current_device();                                                                           \
+    if (dev < 0) return MF_ERR_BAD_ARG;                                                                            \
+    if (!once.done[dev]) {                                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(delta_recurrence_staged_kernel<DPT>,                                    \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
+      if (e != cudaSuccess) return (int)e;                                                                         \
+      once.done[dev] = true;                                                                                       \
+    }                                                                                                              \
+    delta_recurrence_staged_kernel<DPT><<<grid, DR_THREADS, smem, stream>>>(                                       \
+        qkv, beta, ag, ag_ld, state, state_stride, seq_q_start, seq_q_len, slots, o_out, n_heads, n_kv, dim, vdim); \
+  } while (0)
+    if (per <= 4) DS_LAUNCH(4);
+    else if (per <= 8) DS_LAUNCH(8);
+    else if (per <= 16) DS_LAUNCH(16);
+    else DS_LAUNCH(32);
+#undef DS_LAUNCH
+    return (int)cudaGetLastError();
+  }
   if (per <= 4) DR_LAUNCH(4);
   else if (per <= 8) DR_LAUNCH(8);
   else if (per <= 16) DR_LAUNCH(16);

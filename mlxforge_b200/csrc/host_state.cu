@@ -9,7 +9,7 @@ const char* const kNames[MF_K_COUNT] = {
     "stream_rows",      "stream_tmap",      "mid_rows",         "gemm_tc",
     "gemm_tc_swiglu",   "gemm_f32",         "attn_generic", "attn_prefill_mma", "attn_prefill_tc",
     "attn_decode",      "attn_decode_tma",  "attn_decode_tma_merged", "attn_decode_merge",
-    "embed_positions",  "hyper_norm",       "kv_store",         "attn_talking",     "attn_talking_tc",
+    "embed_positions",  "hyper_norm",       "kv_store",         "attn_talking",     "attn_talking_tc", "attn_talking_merge",
     "delta_prepare",    "delta_gates",      "delta_recurrence", "delta_output",
     "moe_route",        "moe_rows",         "moe_combine",      "moe_sort",         "moe_grouped",
 };

@@ -12,8 +12,9 @@
 // w_down [E, H, ff].
 //
 // mf_moe_rows is the kernel for few tokens and for the 32-bit path: a block per (token, chosen
-// expert) streams that expert's matrices once; the chosen experts' outputs are then added in
-// the order of the choice, so a token's result does not depend on what else is in the batch.
+// expert, slice of the expert's columns) streams its part of that expert's matrices once; the
+// chosen experts' outputs are then added in the order of the choice, so a token's result does
+// not depend on what else is in the batch.
 #include "common.cuh"
 
 __device__ __forceinline__ float moe_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
@@ -103,27 +104,32 @@ MF_API int mf_moe_route(const float* z, int T, int E, int n_groups, int keep, in
   return (int)cudaGetLastError();
 }
 
-// ------------------------------------------------------------------ experts, a block per (token, choice)
-// y [T, top, H] 32-bit, not yet weighted.
+// ------------------------------------------------------------------ experts, a block per (token, choice, slice)
+// The expert's ff columns are cut into slices of MOE_SLICE: a block computes the activations of
+// its slice and their share of the down projection, y [T, top, n_slices, H] 32-bit, not yet
+// weighted.  The slices are fixed by ff alone, so a token's sums never depend on the batch.
+#define MOE_SLICE 64
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_rows_kernel(const T* __restrict__ x, const T* __restrict__ w_gu, const T* __restrict__ w_down,
                 const int* __restrict__ ids, float* __restrict__ y, int H, int ff, int top, float limit, float alpha) {
   extern __shared__ float sm[];
   float* xs = sm;            // [H]
-  float* act = sm + H;       // [ff]
+  float* act = sm + H;       // [MOE_SLICE]
   pdl_launch();
   pdl_wait();
-  const int t = blockIdx.x, k = blockIdx.y;
+  const int t = blockIdx.x, k = blockIdx.y, slice = blockIdx.z;
+  const int f0 = slice * MOE_SLICE, fn = min(MOE_SLICE, ff - f0);
   const int e = ids[(long long)t * top + k];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = to_f32<T>(x[(long long)t * H + i]);
   __syncthreads();
   const T* wg = w_gu + (long long)e * 2 * ff * H;
   const T* wu = wg + (long long)ff * H;
-  for (int f = warp; f < ff; f += nwarps) {
-    const T* rg = wg + (long long)f * H;
-    const T* ru = wu + (long long)f * H;
+  for (int f = warp; f < fn; f += nwarps) {
+    const T* rg = wg + (long long)(f0 + f) * H;
+    const T* ru = wu + (long long)(f0 + f) * H;
     float g = 0.f, u = 0.f;
     for (int i = lane; i < H; i += 32) {
       g = fmaf(xs[i], to_f32<T>(rg[i]), g);
@@ -139,68 +145,146 @@ moe_rows_kernel(const T* __restrict__ x, const T* __restrict__ w_gu, const T* __
     }
   }
   __syncthreads();
-  const T* wd = w_down + (long long)e * H * ff;
-  float* yo = y + ((long long)t * top + k) * H;
+  const T* wd = w_down + (long long)e * H * ff + f0;
+  float* yo = y + (((long long)t * top + k) * gridDim.z + slice) * H;
   for (int c = warp; c < H; c += nwarps) {
     const T* rd = wd + (long long)c * ff;
     float a = 0.f;
-    for (int i = lane; i < ff; i += 32) a = fmaf(act[i], to_f32<T>(rd[i]), a);
+    for (int i = lane; i < fn; i += 32) a = fmaf(act[i], to_f32<T>(rd[i]), a);
     a = warp_sum(a);
     if (lane == 0) yo[c] = a;
   }
 }
 
+// The same for bfloat16 in 16-byte pieces (H and ff multiples of 8): a warp per gate/up row with
+// 8 columns a lane and pass, 8 lanes per row of the down projection's slice.
+__device__ __forceinline__ float moe_dot8(const uint4 w, const float* xv) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&w);
+  float a = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const float2 f = __bfloat1622float2(p[j]);
+    a = fmaf(xv[2 * j], f.x, a);
+    a = fmaf(xv[2 * j + 1], f.y, a);
+  }
+  return a;
+}
+
+__global__ void __launch_bounds__(256)
+moe_rows_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu,
+                         const __nv_bfloat16* __restrict__ w_down, const int* __restrict__ ids, float* __restrict__ y,
+                         int H, int ff, int top, float limit, float alpha) {
+  extern __shared__ __align__(16) float sm[];
+  float* xs = sm;            // [H]
+  float* act = sm + H;       // [MOE_SLICE]
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x, k = blockIdx.y, slice = blockIdx.z;
+  const int f0 = slice * MOE_SLICE, fn = min(MOE_SLICE, ff - f0);
+  const int e = ids[(long long)t * top + k];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = __bfloat162float(x[(long long)t * H + i]);
+  if (threadIdx.x < MOE_SLICE) act[threadIdx.x] = 0.f;
+  __syncthreads();
+  const __nv_bfloat16* wg = w_gu + (long long)e * 2 * ff * H;
+  const __nv_bfloat16* wu = wg + (long long)ff * H;
+  for (int f = warp; f < fn; f += nwarps) {
+    const uint4* rg = reinterpret_cast<const uint4*>(wg + (long long)(f0 + f) * H);
+    const uint4* ru = reinterpret_cast<const uint4*>(wu + (long long)(f0 + f) * H);
+    float g = 0.f, u = 0.f;
+    for (int i = lane; i < H / 8; i += 32) {
+      const uint4 a = rg[i], b = ru[i];
+      float xv[8];
+      *reinterpret_cast<float4*>(xv) = *reinterpret_cast<const float4*>(xs + 8 * i);
+      *reinterpret_cast<float4*>(xv + 4) = *reinterpret_cast<const float4*>(xs + 8 * i + 4);
+      g += moe_dot8(a, xv);
+      u += moe_dot8(b, xv);
+    }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    if (lane == 0) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      act[f] = __bfloat162float(__float2bfloat16_rn(g * moe_sigmoid(alpha * g) * (u + 1.0f)));
+    }
+  }
+  __syncthreads();
+  const __nv_bfloat16* wd = w_down + (long long)e * H * ff + f0;
+  float* yo = y + (((long long)t * top + k) * gridDim.z + slice) * H;
+  const int sub = threadIdx.x & 7, row0 = threadIdx.x >> 3;        // 8 lanes a row, 32 rows a pass
+  float av[8];
+  *reinterpret_cast<float4*>(av) = *reinterpret_cast<const float4*>(act + 8 * sub);
+  *reinterpret_cast<float4*>(av + 4) = *reinterpret_cast<const float4*>(act + 8 * sub + 4);
+  for (int c = row0; c < H; c += 32) {
+    float a = 0.f;
+    if (8 * sub < fn) a = moe_dot8(*reinterpret_cast<const uint4*>(wd + (long long)c * ff + 8 * sub), av);
+    a += __shfl_xor_sync(0xffffffffu, a, 1);
+    a += __shfl_xor_sync(0xffffffffu, a, 2);
+    a += __shfl_xor_sync(0xffffffffu, a, 4);
+    if (sub == 0) yo[c] = a;
+  }
+}
+
+MF_API int mf_moe_rows_slices(int ff) { return (ff + MOE_SLICE - 1) / MOE_SLICE; }
+
 MF_API int mf_moe_rows(const void* x, const void* w_gu, const void* w_down, int dtype, const int* ids, float* y, int T,
                        int H, int ff, int top, float limit, float alpha, cudaStream_t stream) {
   if (T <= 0) return 0;
-  const size_t smem = (size_t)(H + ff) * sizeof(float);
+  const size_t smem = (size_t)(H + MOE_SLICE) * sizeof(float);
   if (smem > 200 * 1024 || top > 65535) return MF_ERR_BAD_ARG;
+  const dim3 grid(T, top, mf_moe_rows_slices(ff));
   mf_count(MF_K_MOE_ROWS);
-#define MR_LAUNCH(TT)                                                                                              \
+#define MR_LAUNCH(KERNEL, TT)                                                                                      \
   do {                                                                                                             \
     if (smem > 48 * 1024) {                                                                                        \
-      cudaError_t e = cudaFuncSetAttribute(moe_rows_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
-                                           (int)smem);                                                             \
+      cudaError_t e = cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
       if (e != cudaSuccess) return (int)e;                                                                         \
     }                                                                                                              \
-    return (int)launch_dep(moe_rows_kernel<TT>, dim3(T, top), dim3(256), smem, stream, (const TT*)x,               \
-                           (const TT*)w_gu, (const TT*)w_down, ids, y, H, ff, top, limit, alpha);                  \
+    return (int)launch_dep(KERNEL, grid, dim3(256), smem, stream, (const TT*)x, (const TT*)w_gu, (const TT*)w_down, \
+                           ids, y, H, ff, top, limit, alpha);                                                      \
   } while (0)
-  if (dtype == MF_F32) MR_LAUNCH(float);
-  if (dtype == MF_BF16) MR_LAUNCH(__nv_bfloat16);
+  if (dtype == MF_F32) MR_LAUNCH(moe_rows_kernel<float>, float);
+  if (dtype == MF_BF16) {
+    const bool vec = H % 8 == 0 && ff % 8 == 0 && ((uintptr_t)w_gu & 15) == 0 && ((uintptr_t)w_down & 15) == 0;
+    if (vec) MR_LAUNCH(moe_rows_bf16_vec_kernel, __nv_bfloat16);
+    MR_LAUNCH(moe_rows_kernel<__nv_bfloat16>, __nv_bfloat16);
+  }
 #undef MR_LAUNCH
   return MF_ERR_BAD_DTYPE;
 }
 
 // ------------------------------------------------------------------ the weighted sum of the chosen experts
-// out[t] = sum_k weights[t, k] * y[src(t, k)], k in the order of the choice.  `slot_of` null:
-// src(t, k) = t * top + k; else the row of y that holds the pair (tokens sorted by expert).
+// out[t] = sum_k weights[t, k] * sum_s y[src(t, k) * slices + s], k in the order of the choice,
+// the slices of an expert in their order.  `slot_of` null: src(t, k) = t * top + k; else the row
+// of y that holds the pair (tokens sorted by expert).
 template <typename TO>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, const int* __restrict__ slot_of,
-                   TO* __restrict__ out, int H, int top) {
+                   TO* __restrict__ out, int H, int top, int slices) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x) {
     float a = 0.f;
     for (int k = 0; k < top; k++) {
-      const long long row = slot_of ? slot_of[(long long)t * top + k] : (long long)t * top + k;
-      a = fmaf(weights[(long long)t * top + k], y[row * H + i], a);
+      const long long row = (slot_of ? slot_of[(long long)t * top + k] : (long long)t * top + k) * slices;
+      float part = 0.f;
+      for (int sl = 0; sl < slices; sl++) part += y[(row + sl) * H + i];
+      a = fmaf(weights[(long long)t * top + k], part, a);
     }
     out[(long long)t * H + i] = from_f32<TO>(a);
   }
 }
 
 MF_API int mf_moe_combine(const float* y, const float* weights, const int* slot_of, void* out, int out_dtype, int T,
-                          int H, int top, cudaStream_t stream) {
+                          int H, int top, int slices, cudaStream_t stream) {
   if (T <= 0) return 0;
   mf_count(MF_K_MOE_COMBINE);
   if (out_dtype == MF_F32)
-    return (int)launch_dep(moe_combine_kernel<float>, dim3(T), dim3(256), 0, stream, y, weights, slot_of, (float*)out,
-                           H, top);
+    return (int)launch_dep(moe_combine_kernel<float>, dim3(T, (H + 255) / 256), dim3(256), 0, stream, y, weights, slot_of, (float*)out,
+                           H, top, slices);
   if (out_dtype == MF_BF16)
-    return (int)launch_dep(moe_combine_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, y, weights, slot_of,
-                           (__nv_bfloat16*)out, H, top);
+    return (int)launch_dep(moe_combine_kernel<__nv_bfloat16>, dim3(T, (H + 255) / 256), dim3(256), 0, stream, y, weights, slot_of,
+                           (__nv_bfloat16*)out, H, top, slices);
   return MF_ERR_BAD_DTYPE;
 }

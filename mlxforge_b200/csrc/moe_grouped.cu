@@ -11,16 +11,18 @@
 //                   products of the row's token (gathered by row_token), bfloat16.
 //   mf_moe_grouped_down  y[row] = Wd_e act[row], 32-bit.
 //
-// Both products are mma.sync m16n8k16 tiles of 64 rows x 64 columns, four warps, K in steps of 32
-// through shared memory.  The launches cover the largest possible number of tiles (known on the
+// Both products are mma.sync m16n8k16 tiles of 64 rows x 64 columns, four warps, K in steps of 64
+// through two cp.async stages of shared memory: the next step's operands are on their way while
+// this step's are multiplied.  The launches cover the largest possible number of tiles (known on the
 // host: pairs / 64 + experts); blocks beyond the count the sort kernel wrote return at once, so a
 // step's launches do not depend on its data.
 #include "common.cuh"
 
 #define MG_BM 64
 #define MG_BN 64
-#define MG_BK 32
+#define MG_BK 64
 #define MG_LD (MG_BK + 8)
+#define MG_STAGES 2
 #define MG_MAX_EXPERTS 1024
 
 __device__ __forceinline__ void mg_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -71,35 +73,52 @@ MF_API int mf_moe_sort(const int* ids, int T, int E, int top, int* slot_of, int*
   return (int)cudaGetLastError();
 }
 
+__device__ __forceinline__ void mg_cp16(void* smem, const void* gmem) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(addr), "l"(gmem) : "memory");
+}
+
 // One 64 x 64 tile: acc += A[64 rows, K] * B[64 rows of W, K]^T, A rows given by pointers.
 // `arow(r)` -> pointer to row r of A (or null), `brow(n)` -> pointer to row n of W (or null).
+// As: [MG_STAGES][64][MG_LD], Bs: [MG_STAGES][NB * 64][MG_LD].
 template <int NB, typename ARow, typename BRow>
 __device__ __forceinline__ void mg_tile(float (&acc)[NB][MG_BN / 8][4], int K, ARow arow, BRow brow,
                                         __nv_bfloat16* As, __nv_bfloat16* Bs) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r0 = lane >> 2, c2 = (lane & 3) * 2;
-  for (int k0 = 0; k0 < K; k0 += MG_BK) {
-    __syncthreads();
-    // 64 rows x 32 columns = 256 pieces of 16 bytes per operand
+  auto load = [&](int k0, int stage) {
+    __nv_bfloat16* Ad = As + (size_t)stage * MG_BM * MG_LD;
+    __nv_bfloat16* Bd = Bs + (size_t)stage * NB * MG_BN * MG_LD;
     for (int i = tid; i < MG_BM * (MG_BK / 8); i += blockDim.x) {
       const int r = i / (MG_BK / 8), c = (i - r * (MG_BK / 8)) * 8;
       const __nv_bfloat16* p = arow(r);
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (p && k0 + c < K) v = *reinterpret_cast<const uint4*>(p + k0 + c);
-      *reinterpret_cast<uint4*>(As + r * MG_LD + c) = v;
+      if (p && k0 + c < K) mg_cp16(Ad + r * MG_LD + c, p + k0 + c);
+      else *reinterpret_cast<uint4*>(Ad + r * MG_LD + c) = make_uint4(0, 0, 0, 0);
     }
     for (int i = tid; i < NB * MG_BN * (MG_BK / 8); i += blockDim.x) {
       const int n = i / (MG_BK / 8), c = (i - n * (MG_BK / 8)) * 8;
       const __nv_bfloat16* p = brow(n);
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (p && k0 + c < K) v = *reinterpret_cast<const uint4*>(p + k0 + c);
-      *reinterpret_cast<uint4*>(Bs + n * MG_LD + c) = v;
+      if (p && k0 + c < K) mg_cp16(Bd + n * MG_LD + c, p + k0 + c);
+      else *reinterpret_cast<uint4*>(Bd + n * MG_LD + c) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  load(0, 0);
+  int stage = 0;
+  for (int k0 = 0; k0 < K; k0 += MG_BK, stage ^= 1) {
+    if (k0 + MG_BK < K) {
+      load(k0 + MG_BK, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     }
     __syncthreads();
+    const __nv_bfloat16* Ac = As + (size_t)stage * MG_BM * MG_LD;
+    const __nv_bfloat16* Bc = Bs + (size_t)stage * NB * MG_BN * MG_LD;
 #pragma unroll
     for (int kk = 0; kk < MG_BK; kk += 16) {
       uint32_t af[4];
-      const __nv_bfloat16* ar = As + (warp * 16 + r0) * MG_LD + kk + c2;
+      const __nv_bfloat16* ar = Ac + (warp * 16 + r0) * MG_LD + kk + c2;
       af[0] = *reinterpret_cast<const uint32_t*>(ar);
       af[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * MG_LD);
       af[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
@@ -108,11 +127,12 @@ __device__ __forceinline__ void mg_tile(float (&acc)[NB][MG_BN / 8][4], int K, A
       for (int b = 0; b < NB; b++) {
 #pragma unroll
         for (int nt = 0; nt < MG_BN / 8; nt++) {
-          const __nv_bfloat16* br = Bs + (b * MG_BN + nt * 8 + r0) * MG_LD + kk + c2;
+          const __nv_bfloat16* br = Bc + (b * MG_BN + nt * 8 + r0) * MG_LD + kk + c2;
           mg_mma(acc[b][nt], af, *reinterpret_cast<const uint32_t*>(br), *reinterpret_cast<const uint32_t*>(br + 8));
         }
       }
     }
+    __syncthreads();       // the stage is read: the load after the next may overwrite it
   }
 }
 
@@ -120,8 +140,9 @@ __global__ void __launch_bounds__(128)
 moe_grouped_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu,
                       const int* __restrict__ row_token, const int* __restrict__ meta, const int* __restrict__ tiles,
                       __nv_bfloat16* __restrict__ act, int H, int ff, float limit, float alpha) {
-  __shared__ __align__(16) __nv_bfloat16 As[MG_BM * MG_LD];
-  __shared__ __align__(16) __nv_bfloat16 Bs[2 * MG_BN * MG_LD];
+  extern __shared__ __align__(16) __nv_bfloat16 mg_smem[];
+  __nv_bfloat16* As = mg_smem;
+  __nv_bfloat16* Bs = mg_smem + MG_STAGES * MG_BM * MG_LD;
   if ((int)blockIdx.x >= meta[0]) return;
   const int e = tiles[3 * blockIdx.x], row_first = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
   const int n0 = blockIdx.y * MG_BN;
@@ -166,8 +187,9 @@ __global__ void __launch_bounds__(128)
 moe_grouped_down_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bfloat16* __restrict__ w_down,
                         const int* __restrict__ meta, const int* __restrict__ tiles, float* __restrict__ y, int H,
                         int ff) {
-  __shared__ __align__(16) __nv_bfloat16 As[MG_BM * MG_LD];
-  __shared__ __align__(16) __nv_bfloat16 Bs[MG_BN * MG_LD];
+  extern __shared__ __align__(16) __nv_bfloat16 mg_smem[];
+  __nv_bfloat16* As = mg_smem;
+  __nv_bfloat16* Bs = mg_smem + MG_STAGES * MG_BM * MG_LD;
   if ((int)blockIdx.x >= meta[0]) return;
   const int e = tiles[3 * blockIdx.x], row_first = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
   const int n0 = blockIdx.y * MG_BN;
@@ -205,7 +227,16 @@ MF_API int mf_moe_grouped_up(const void* x, const void* w_gu, const int* row_tok
   if (!mf_moe_grouped_ok(H, ff, E)) return MF_ERR_BAD_ARG;
   dim3 grid(mf_moe_grouped_max_tiles(T, top, E), (ff + MG_BN - 1) / MG_BN);
   mf_count(MF_K_MOE_GROUPED);
-  moe_grouped_up_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gu, row_token, meta,
+  const size_t smem = (size_t)MG_STAGES * (MG_BM + 2 * MG_BN) * MG_LD * sizeof(__nv_bfloat16);
+  static DeviceOnce once;
+  const int dev = mf_current_device();
+  if (dev < 0) return MF_ERR_BAD_ARG;
+  if (!once.done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(moe_grouped_up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    once.done[dev] = true;
+  }
+  moe_grouped_up_kernel<<<grid, 128, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gu, row_token, meta,
                                                   tiles, (__nv_bfloat16*)act, H, ff, limit, alpha);
   return (int)cudaGetLastError();
 }
@@ -216,7 +247,8 @@ MF_API int mf_moe_grouped_down(const void* act, const void* w_down, const int* m
   if (!mf_moe_grouped_ok(H, ff, E)) return MF_ERR_BAD_ARG;
   dim3 grid(mf_moe_grouped_max_tiles(T, top, E), (H + MG_BN - 1) / MG_BN);
   mf_count(MF_K_MOE_GROUPED);
-  moe_grouped_down_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, meta, tiles,
+  const size_t smem = (size_t)MG_STAGES * (MG_BM + MG_BN) * MG_LD * sizeof(__nv_bfloat16);
+  moe_grouped_down_kernel<<<grid, 128, smem, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, meta, tiles,
                                                     y, H, ff);
   return (int)cudaGetLastError();
 }

@@ -475,7 +475,8 @@ def moe_route(z: torch.Tensor, n_groups: int, keep: int, top: int, route_scale: 
 
 def moe_rows(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, y: torch.Tensor,
              limit: float, alpha: float) -> None:
-    """y [T, top, H] (32-bit) = each chosen expert's output for its token, not yet weighted."""
+    """y [T, top, moe_rows_slices(ff), H] (32-bit) = each chosen expert's output for its token, in the
+    partial sums of the slices its columns are cut into, not yet weighted."""
     _need_cuda(x, w_gu, w_down, ids, y)
     T, H = x.shape
     check(library().mf_moe_rows(x.data_ptr(), w_gu.data_ptr(), w_down.data_ptr(), dtype_code(x), ids.data_ptr(),
@@ -483,11 +484,17 @@ def moe_rows(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: tor
           "moe_rows")
 
 
-def moe_combine(y: torch.Tensor, weights: torch.Tensor, slot_of: Optional[torch.Tensor], out: torch.Tensor) -> None:
+def moe_rows_slices(ff: int) -> int:
+    """Partial sums per (token, chosen expert) that ``moe_rows`` writes for experts ``ff`` wide."""
+    return int(library().mf_moe_rows_slices(ff))
+
+
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, slot_of: Optional[torch.Tensor], out: torch.Tensor,
+                slices: int = 1) -> None:
     _need_cuda(y, weights, slot_of, out)
     T, H = out.shape
     check(library().mf_moe_combine(y.data_ptr(), weights.data_ptr(), _ptr(slot_of), out.data_ptr(), dtype_code(out),
-                                   T, H, weights.shape[1], _stream()), "moe_combine")
+                                   T, H, weights.shape[1], slices, _stream()), "moe_combine")
 
 
 def attention_talking_tc_ok(n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int) -> bool:
@@ -511,6 +518,32 @@ def attention_talking_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                                             table_row0, seq_q_len.shape[0], max_q_len, n_heads, n_kv, dim, vdim,
                                             block_table.data_ptr(), block_table.shape[1], page_size, scale, softcap,
                                             _ptr(talk), window, chunk, _stream()), "attention_talking_tc")
+
+
+def attention_talking_splits(max_keys: int) -> int:
+    """Key splits of a decode launch when no query sees more than ``max_keys`` keys."""
+    return int(library().mf_attention_talking_splits(max_keys))
+
+
+def attention_talking_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                             seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, seq_ctx_len: torch.Tensor,
+                             block_table: torch.Tensor, page_size: int, n_heads: int, n_kv: int, dim: int, vdim: int,
+                             scale: float, softcap: float, talk: Optional[torch.Tensor], window: int, chunk: int,
+                             splits: int, part_o: torch.Tensor, part_ml: torch.Tensor) -> None:
+    """Talking-heads attention of sequences that bring one token each (rows 0.. of the block table),
+    bfloat16: the tensor-core kernel over splits of the keys, then the merge of the splits."""
+    _need_cuda(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, block_table, talk, part_o, part_ml)
+    n = q.shape[0]
+    if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
+        raise KernelError("attention_talking_decode: bfloat16 only")
+    if part_o.numel() < n * splits * n_heads * vdim or part_ml.numel() < n * splits * n_heads * 2:
+        raise KernelError("attention_talking_decode: scratch too small")
+    check(library().mf_attention_talking_decode(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+                                                seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_ctx_len.data_ptr(),
+                                                n, n_heads, n_kv, dim, vdim, block_table.data_ptr(),
+                                                block_table.shape[1], page_size, scale, softcap, _ptr(talk), window,
+                                                chunk, splits, part_o.data_ptr(), part_ml.data_ptr(), _stream()),
+          "attention_talking_decode", launches=2)
 
 
 def moe_grouped_ok(hidden: int, ff: int, n_experts: int) -> bool:

@@ -92,9 +92,10 @@ class RoutedExperts(FeedForward):
         if (x.dtype == torch.bfloat16 and T >= self.grouped_min_tokens
                 and ops.moe_grouped_ok(self.hidden, self.ff, self.n_experts)):
             return self.forward_grouped(x, ids, weights, out)
-        y = rt.buffer("moe.y", (T, self.top, self.hidden), torch.float32)
+        slices = ops.moe_rows_slices(self.ff)
+        y = rt.buffer("moe.y", (T, self.top * slices, self.hidden), torch.float32)
         ops.moe_rows(x, self.w_gu, self.w_down, ids, y, self.limit, self.alpha)
-        ops.moe_combine(y, weights, None, out)
+        ops.moe_combine(y, weights, None, out, slices)
         return out
 
     def forward_grouped(self, x, ids, weights, out):

@@ -111,17 +111,29 @@ class TalkingAttention(Mixer):
 
 def talking_paged_attention(rt, batch, q, lane, out, m: TalkingAttention) -> None:
     """The kernel is chosen by dtype and by how many tokens a sequence brings, as for the plain
-    attention: the block-per-token kernel for the 32-bit path and for single decoded tokens, the
-    tensor-core kernel for portions of prompts in bfloat16 where it takes the sizes."""
+    attention.  bfloat16 with sizes the tensor-core kernel takes: the sequences that bring one token
+    (the batch lays them out first) go through it with their keys cut into splits and a merge, the
+    portions of prompts with a block per 16 queries.  Everything else (the 32-bit path, other
+    sizes) takes the kernel with a block per token."""
     table = batch.block_table(lane.group)
-    nd = batch.n_decode if q.dtype == torch.bfloat16 else batch.n_tokens
-    tc = (nd < batch.n_tokens and ops.attention_talking_tc_ok(m.n_heads, m.n_kv, m.dim, m.vdim, lane.page_size))
+    tc = q.dtype == torch.bfloat16 and ops.attention_talking_tc_ok(m.n_heads, m.n_kv, m.dim, m.vdim, lane.page_size)
     if not tc:
-        nd = batch.n_tokens
+        ops.attention_talking(q, lane.k, lane.v, out, batch.positions, batch.seq_of_token, table, lane.page_size,
+                              m.n_heads, m.n_kv, m.dim, m.vdim, m.scale, m.softcap, m.talk, m.window, m.chunk)
+        return
+    nd = batch.n_decode
     if nd > 0:
-        ops.attention_talking(q[:nd], lane.k, lane.v, out[:nd], batch.positions[:nd], batch.seq_of_token[:nd], table,
-                              lane.page_size, m.n_heads, m.n_kv, m.dim, m.vdim, m.scale, m.softcap, m.talk,
-                              m.window, m.chunk)
+        max_keys = batch.max_ctx
+        if m.chunk:
+            max_keys = min(max_keys, m.chunk)
+        if m.window:
+            max_keys = min(max_keys, m.window)
+        splits = ops.attention_talking_splits(max_keys)
+        part_o = rt.buffer("tattn.part_o", (nd * splits * m.n_heads * m.vdim,), torch.float32)
+        part_ml = rt.buffer("tattn.part_ml", (nd * splits * m.n_heads * 2,), torch.float32)
+        ops.attention_talking_decode(q[:nd], lane.k, lane.v, out[:nd], batch.seq_q_start[:nd], batch.seq_q_len[:nd],
+                                     batch.seq_ctx_len[:nd], table, lane.page_size, m.n_heads, m.n_kv, m.dim, m.vdim,
+                                     m.scale, m.softcap, m.talk, m.window, m.chunk, splits, part_o, part_ml)
     if nd < batch.n_tokens:
         ops.attention_talking_tc(q, lane.k, lane.v, out, batch.seq_q_start[nd:], batch.seq_q_len[nd:],
                                  batch.seq_ctx_len[nd:], nd, max(batch.q_len[nd:]), table, lane.page_size,

@@ -504,7 +504,7 @@ def test_serving_shapes_take_the_fast_kernels(models, tmp_path):
     ran = _check(models, "C", False, "bfloat16", TT.decode_tail(reqs, tail=8), tmp_path)
     for k in ("hyper_norm", "delta_recurrence", "moe_route", "embed_positions", "kv_store"):
         assert ran.get(k, 0) > 0, (k, ran)
-    assert ran.get("attn_talking_tc", 0) > 0 and ran.get("attn_talking", 0) > 0, ran
+    assert ran.get("attn_talking_tc", 0) > 0 and ran.get("attn_talking_merge", 0) > 0, ran
     assert ran.get("moe_grouped", 0) > 0 and ran.get("moe_rows", 0) > 0, ran
 
 
