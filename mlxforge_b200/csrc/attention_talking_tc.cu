@@ -96,7 +96,7 @@ talking_attention_tc_kernel(const TtArgs a) {
   __nv_bfloat16* Ks = Qs + (size_t)H * TT_BM * qs_ld;                       // [G][32][qs_ld]
   __nv_bfloat16* Vs = Ks + (size_t)G * TT_BN * qs_ld;                       // [G][32][vs_ld]
   float* sc = reinterpret_cast<float*>(Vs + (size_t)G * TT_BN * vs_ld);     // [H][16][sc_ld]
-  float* tk = sc + (size_t)H * TT_BM * sc_ld;                               // [H][H]
+  float* tk = sc + (size_t)H * TT_BM * sc_ld;                               // [H from][MAXH to], zero beyond H
 
   const int tid = threadIdx.x, nthreads = blockDim.x;
   const int lane = tid & 31, warp = tid >> 5;          // warp = head
@@ -111,7 +111,10 @@ talking_attention_tc_kernel(const TtArgs a) {
     if (r < rows) v = *reinterpret_cast<const uint4*>(a.q + ((long long)(q_start + row0 + r) * H + h) * dim + c);
     *reinterpret_cast<uint4*>(Qs + ((size_t)h * TT_BM + r) * qs_ld + c) = v;
   }
-  for (int i = tid; i < H * H; i += nthreads) tk[i] = a.talk ? a.talk[i] : ((i / H == i % H) ? 1.f : 0.f);
+  for (int i = tid; i < H * MAXH; i += nthreads) {
+    const int g = i / MAXH, h = i - g * MAXH;
+    tk[i] = h < H ? (a.talk ? a.talk[h * H + g] : (h == g ? 1.f : 0.f)) : 0.f;
+  }
 
   // the first key any query of the tile sees: that of its first query
   int lo0 = 0;
@@ -126,6 +129,13 @@ talking_attention_tc_kernel(const TtArgs a) {
   const int g_own = warp / rep;
   const bool has_head = warp < H;
 
+  // how this thread walks over the pieces of a key tile
+  int kc, kcs, kr0, krs;
+  if (nthreads % dv8 == 0) {
+    kc = (tid % dv8) * 8; kcs = dim; kr0 = tid / dv8; krs = nthreads / dv8;
+  } else {                   // a row at a time, its pieces in turn
+    kc = 0; kcs = 8; kr0 = tid; krs = nthreads;
+  }
   int k_first = (lo0 / TT_BN) * TT_BN, k_last = pos_last;
   if (a.splits > 0) {      // this block's share: tiles [z, z + 1) * TT_SPLIT_TILES of the sequence
     const int span = TT_SPLIT_TILES * TT_BN;
@@ -137,21 +147,28 @@ talking_attention_tc_kernel(const TtArgs a) {
     __syncthreads();       // the tile before is done with Ks, Vs and sc (and Qs, tk are written)
     // keys and values of the tile: two granules of 16 positions, each inside one page
     long long pg[TT_BN / 16];
+    int sl[TT_BN / 16];
 #pragma unroll
     for (int gq = 0; gq < TT_BN / 16; gq++) {
       const int p0 = k0 + 16 * gq;
-      pg[gq] = (p0 <= pos_last && p0 + 15 >= lo0) ? (long long)table[p0 / a.page_size] : -1;
+      const int blk = p0 / a.page_size;
+      sl[gq] = p0 - blk * a.page_size;
+      pg[gq] = (p0 <= pos_last && p0 + 15 >= lo0) ? (long long)table[blk] : -1;
     }
-    for (int i = tid; i < G * TT_BN * dv8; i += nthreads) {
-      const int row = i / dv8, c = (i - row * dv8) * 8;
-      const int g = row / TT_BN, j = row - g * TT_BN;
-      const int pj = k0 + j;
-      __nv_bfloat16* dst = Ks + (size_t)row * qs_ld + c;
-      const long long page = (j >> 4) ? pg[1] : pg[0];
-      if (pj >= lo0 && pj <= pos_last && page >= 0)
-        tt_cp_async16(dst, a.k_pool + ((page * G + g) * a.page_size + (pj % a.page_size)) * dim + c);
-      else
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    // a thread copies the same 16-byte column of every row it takes (kc, row stride krs), where the
+    // block's threads divide evenly among a row's pieces; else piece by piece
+    for (int row = kr0; row < G * TT_BN; row += krs) {
+      for (int c = kc; c < dim; c += kcs) {
+        const int g = row / TT_BN, j = row - g * TT_BN;
+        const int pj = k0 + j;
+        __nv_bfloat16* dst = Ks + (size_t)row * qs_ld + c;
+        const long long page = (j >> 4) ? pg[1] : pg[0];
+        const int slot = ((j >> 4) ? sl[1] : sl[0]) + (j & 15);
+        if (pj >= lo0 && pj <= pos_last && page >= 0)
+          tt_cp_async16(dst, a.k_pool + ((page * G + g) * a.page_size + slot) * dim + c);
+        else
+          *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
     }
     for (int i = tid; i < G * TT_BN * (VDIM / 8); i += nthreads) {
       const int row = i / (VDIM / 8), c = (i - row * (VDIM / 8)) * 8;
@@ -159,8 +176,9 @@ talking_attention_tc_kernel(const TtArgs a) {
       const int pj = k0 + j;
       __nv_bfloat16* dst = Vs + (size_t)row * vs_ld + c;
       const long long page = (j >> 4) ? pg[1] : pg[0];
+      const int slot = ((j >> 4) ? sl[1] : sl[0]) + (j & 15);
       if (pj >= lo0 && pj <= pos_last && page >= 0)
-        tt_cp_async16(dst, a.v_pool + ((page * G + g) * a.page_size + (pj % a.page_size)) * VDIM + c);
+        tt_cp_async16(dst, a.v_pool + ((page * G + g) * a.page_size + slot) * VDIM + c);
       else
         *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
@@ -210,13 +228,18 @@ talking_attention_tc_kernel(const TtArgs a) {
       if (a.talk) {
         for (int g = 0; g < H; g++) {
           const float2 sg = *reinterpret_cast<const float2*>(sc + ((size_t)g * TT_BM + r) * sc_ld + j2);
+          const float4* tg = reinterpret_cast<const float4*>(tk + g * MAXH);
 #pragma unroll
-          for (int h = 0; h < MAXH; h++) {
-            if (h < H) {
-              const float t = tk[h * H + g];
-              acc[h][0] = fmaf(t, sg.x, acc[h][0]);
-              acc[h][1] = fmaf(t, sg.y, acc[h][1]);
-            }
+          for (int h4 = 0; h4 < MAXH / 4; h4++) {       // heads beyond H have weight zero and are not stored
+            const float4 t = tg[h4];
+            acc[4 * h4][0] = fmaf(t.x, sg.x, acc[4 * h4][0]);
+            acc[4 * h4][1] = fmaf(t.x, sg.y, acc[4 * h4][1]);
+            acc[4 * h4 + 1][0] = fmaf(t.y, sg.x, acc[4 * h4 + 1][0]);
+            acc[4 * h4 + 1][1] = fmaf(t.y, sg.y, acc[4 * h4 + 1][1]);
+            acc[4 * h4 + 2][0] = fmaf(t.z, sg.x, acc[4 * h4 + 2][0]);
+            acc[4 * h4 + 2][1] = fmaf(t.z, sg.y, acc[4 * h4 + 2][1]);
+            acc[4 * h4 + 3][0] = fmaf(t.w, sg.x, acc[4 * h4 + 3][0]);
+            acc[4 * h4 + 3][1] = fmaf(t.w, sg.y, acc[4 * h4 + 3][1]);
           }
         }
       } else {
@@ -337,7 +360,7 @@ talking_attention_tc_kernel(const TtArgs a) {
 
 static size_t tt_smem_bytes(int H, int G, int dim, int vdim) {
   return (size_t)(H * TT_BM + G * TT_BN) * (dim + 8) * 2 + (size_t)G * TT_BN * (vdim + 8) * 2 +
-         (size_t)H * TT_BM * (TT_BN + TT_SPAD) * 4 + (size_t)H * H * 4;
+         (size_t)H * TT_BM * (TT_BN + TT_SPAD) * 4 + (size_t)H * 16 * 4;
 }
 
 // 1 if the kernel takes these sizes

@@ -30,7 +30,7 @@ __device__ __forceinline__ float dr_softplus(float x) { return x > 20.f ? x : lo
 // activations that are only copied (rounded to the compute dtype) into `low` [T, n_low].
 // qkv_out [T, C] 32-bit: queries (unit, scaled), keys (unit), values.  beta_out [T, n_heads].
 template <typename TL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 delta_prepare_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ conv_w, int taps,
                      const float* __restrict__ state, long long state_stride, long long conv_off,
                      const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -340,7 +340,7 @@ MF_API int mf_delta_prepare(const float* proj, int ld, const float* conv_w, int 
                                            (int)smem);                                                             \
       if (e != cudaSuccess) return (int)e;                                                                         \
     }                                                                                                              \
-    delta_prepare_kernel<TL><<<T, 256, smem, stream>>>(proj, ld, conv_w, taps, state, state_stride, conv_off,      \
+    delta_prepare_kernel<TL><<<T, T <= 64 ? 1024 : 256, smem, stream>>>(proj, ld, conv_w, taps, state, state_stride, conv_off,      \
                                                        positions, seq_of_token, seq_q_start, slots, qkv_out,       \
                                                        beta_out, (TL*)low, n_low, n_heads, n_kv, dim, vdim);       \
   } while (0)

@@ -133,6 +133,107 @@ hyper_update_norm_kernel(float* __restrict__ streams, const TD* __restrict__ del
   for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>(u[i] * ginv[i / gs] * w[i]);
 }
 
+// The same with the channels in groups of four (H and the group size multiples of 4): 16-byte
+// accesses to the streams, and each thread keeps its values of u in registers between the passes.
+template <typename TD, typename TO, int NV>
+__global__ void __launch_bounds__(HS_THREADS)
+hyper_update_norm_vec_kernel(float* __restrict__ streams, const TD* __restrict__ delta,
+                             const float* __restrict__ delta_bias, const float* __restrict__ mix,
+                             const float* __restrict__ wout, const float* __restrict__ win,
+                             const float* __restrict__ w, float eps, int groups, TO* __restrict__ out,
+                             const int* __restrict__ rows, int H, int S) {
+  __shared__ float red[32];
+  __shared__ float cm[HS_MAX_STREAMS * HS_MAX_STREAMS], co[HS_MAX_STREAMS], ci[HS_MAX_STREAMS];
+  __shared__ float gsum[HS_MAX_GROUPS];
+  pdl_launch();
+  if (threadIdx.x < S * S) cm[threadIdx.x] = mix ? mix[threadIdx.x] : ((threadIdx.x / S == threadIdx.x % S) ? 1.f : 0.f);
+  if (threadIdx.x < S) {
+    co[threadIdx.x] = wout ? wout[threadIdx.x] : 1.f;
+    ci[threadIdx.x] = win ? win[threadIdx.x] : 1.f;
+  }
+  if (threadIdx.x < groups) gsum[threadIdx.x] = 0.f;
+  pdl_wait();
+  __syncthreads();
+  const int r = blockIdx.x;
+  const long long src = rows ? rows[r] : r;
+  float* x = streams + src * S * H;
+  const TD* d = delta ? delta + src * H : nullptr;
+  const int gs = H / groups;
+  float u[NV][4];
+#pragma unroll
+  for (int j = 0; j < NV; j++) {
+    const int i = (j * HS_THREADS + threadIdx.x) * 4;
+    u[j][0] = u[j][1] = u[j][2] = u[j][3] = 0.f;
+    if (i < H) {
+      float xs[HS_MAX_STREAMS][4];
+#pragma unroll
+      for (int s = 0; s < HS_MAX_STREAMS; s++) {
+        if (s < S) {
+          const float4 v = *reinterpret_cast<const float4*>(x + (long long)s * H + i);
+          xs[s][0] = v.x; xs[s][1] = v.y; xs[s][2] = v.z; xs[s][3] = v.w;
+        }
+      }
+      if (d) {
+        float y[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) y[e] = to_f32<TD>(d[i + e]) + (delta_bias ? delta_bias[i + e] : 0.f);
+        float nx[HS_MAX_STREAMS][4];
+#pragma unroll
+        for (int t = 0; t < HS_MAX_STREAMS; t++) {
+          if (t < S) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              float a = 0.f;
+#pragma unroll
+              for (int s = 0; s < HS_MAX_STREAMS; s++)
+                if (s < S) a = fmaf(cm[s * S + t], xs[s][e], a);
+              nx[t][e] = fmaf(co[t], y[e], a);
+            }
+            if (!rows)
+              *reinterpret_cast<float4*>(x + (long long)t * H + i) = make_float4(nx[t][0], nx[t][1], nx[t][2], nx[t][3]);
+          }
+        }
+#pragma unroll
+        for (int s = 0; s < HS_MAX_STREAMS; s++)
+          if (s < S) { xs[s][0] = nx[s][0]; xs[s][1] = nx[s][1]; xs[s][2] = nx[s][2]; xs[s][3] = nx[s][3]; }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        float a = 0.f;
+#pragma unroll
+        for (int s = 0; s < HS_MAX_STREAMS; s++)
+          if (s < S) a = fmaf(ci[s], xs[s][e], a);
+        u[j][e] = a;
+      }
+    }
+  }
+  // sums of squares per group, in a fixed order: group by group, each a block-wide sum
+  for (int g = 0; g < groups; g++) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+      const int i = (j * HS_THREADS + threadIdx.x) * 4;
+      if (i < H && i / gs == g) ss += u[j][0] * u[j][0] + u[j][1] * u[j][1] + u[j][2] * u[j][2] + u[j][3] * u[j][3];
+    }
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) gsum[g] = 1.0f / sqrtf(ss / (float)gs + eps);
+  }
+  __syncthreads();
+  TO* o = out + (long long)r * H;
+#pragma unroll
+  for (int j = 0; j < NV; j++) {
+    const int i = (j * HS_THREADS + threadIdx.x) * 4;
+    if (i < H) {
+      const float inv = gsum[i / gs];
+      const float4 wv = *reinterpret_cast<const float4*>(w + i);
+      o[i] = from_f32<TO>(u[j][0] * inv * wv.x);
+      o[i + 1] = from_f32<TO>(u[j][1] * inv * wv.y);
+      o[i + 2] = from_f32<TO>(u[j][2] * inv * wv.z);
+      o[i + 3] = from_f32<TO>(u[j][3] * inv * wv.w);
+    }
+  }
+}
+
 MF_API int mf_hyper_update_norm(float* streams, const void* delta, int delta_dtype, const float* delta_bias,
                                 const float* mix, const float* wout, const float* win, const float* w, float eps,
                                 int groups, void* out, int out_dtype, const int* rows, int n, int H, int S,
@@ -144,6 +245,16 @@ MF_API int mf_hyper_update_norm(float* streams, const void* delta, int delta_dty
   mf_count(MF_K_HYPER_NORM);
 #define HS_LAUNCH(TD, TO)                                                                                        \
   do {                                                                                                           \
+    const bool vec = H % 4 == 0 && (H / groups) % 4 == 0 && H <= 4 * HS_THREADS * 8 &&                           \
+                     ((uintptr_t)streams & 15) == 0 && ((uintptr_t)w & 15) == 0;                                 \
+    if (vec && H <= 4 * HS_THREADS * 2)                                                                          \
+      return (int)launch_dep(hyper_update_norm_vec_kernel<TD, TO, 2>, dim3(n), dim3(HS_THREADS), 0, stream,      \
+                             streams, (const TD*)delta, delta_bias, mix, wout, win, w, eps, groups, (TO*)out,    \
+                             rows, H, S);                                                                        \
+    if (vec)                                                                                                     \
+      return (int)launch_dep(hyper_update_norm_vec_kernel<TD, TO, 8>, dim3(n), dim3(HS_THREADS), 0, stream,      \
+                             streams, (const TD*)delta, delta_bias, mix, wout, win, w, eps, groups, (TO*)out,    \
+                             rows, H, S);                                                                        \
     if (smem > 48 * 1024) {                                                                                      \
       cudaError_t e = cudaFuncSetAttribute(hyper_update_norm_kernel<TD, TO>,                                     \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
