@@ -223,26 +223,46 @@ delta_recurrence_staged_kernel(const float* __restrict__ qkv, const float* __res
   }
   const int d4 = dim / 4;
   const int n_chunks = (n + DR_CHUNK - 1) / DR_CHUNK;
+  // what this thread copies of every stage, worked out once: up to NP 16-byte pieces of the q, k and
+  // g rows (source pointer for the first stage, it moves on by a stage's tokens; place in the stage),
+  // one piece of the values and one beta
+  constexpr int NP = (DR_CHUNK * 3 * (DP / 4) + DR_THREADS - 1) / DR_THREADS;
+  const float* src[NP];
+  int dst[NP], ptok[NP], pstep[NP];
+#pragma unroll
+  for (int p = 0; p < NP; p++) {
+    const int i = threadIdx.x + p * DR_THREADS;
+    ptok[p] = DR_CHUNK;                                   // no piece
+    src[p] = qkv;
+    dst[p] = 0;
+    pstep[p] = 0;
+    if (i < DR_CHUNK * 3 * d4) {
+      const int tok = i / (3 * d4), rem = i - tok * 3 * d4;
+      const int which = rem / d4, c = (rem - which * d4) * 4;
+      const long long t = start + tok;
+      ptok[p] = tok;
+      src[p] = which == 0 ? qkv + t * C + kvh * dim + c
+             : which == 1 ? qkv + t * C + (n_kv + kvh) * dim + c
+                          : ag + t * ag_ld + h * dim + c;
+      pstep[p] = DR_CHUNK * (which == 2 ? ag_ld : C);
+      dst[p] = tok * TOK + which * DP + c;
+    }
+  }
+  const int vtok = threadIdx.x / (DR_COLS / 4), vc = (threadIdx.x % (DR_COLS / 4)) * 4;      // 32 threads: 8 tokens x 4 pieces
+  const bool vcopy = threadIdx.x < DR_CHUNK * (DR_COLS / 4) && col0 + vc < vdim;
+  const float* vsrc = qkv + (long long)(start + vtok) * C + 2 * n_kv * dim + h * vdim + col0 + vc;
+  const bool bcopy = threadIdx.x >= 64 && threadIdx.x < 64 + DR_CHUNK;
+  const int btok = threadIdx.x - 64;
+  const float* bsrc = beta + (long long)(start + btok) * n_heads + h;
   auto issue = [&](int chunk) {
     if (chunk < n_chunks) {
       float* st = dr_sm + (size_t)(chunk % DR_STAGES) * DR_CHUNK * TOK;
-      const int t0 = start + chunk * DR_CHUNK, nt = min(DR_CHUNK, n - chunk * DR_CHUNK);
-      for (int i = threadIdx.x; i < nt * 3 * d4; i += DR_THREADS) {
-        const int tok = i / (3 * d4), rem = i - tok * 3 * d4;
-        const int which = rem / d4, c = (rem - which * d4) * 4;
-        const long long t = t0 + tok;
-        const float* src = which == 0 ? qkv + t * C + kvh * dim + c
-                         : which == 1 ? qkv + t * C + (n_kv + kvh) * dim + c
-                                      : ag + t * ag_ld + h * dim + c;
-        dr_cp16(st + tok * TOK + which * DP + c, src);
-      }
-      for (int i = threadIdx.x; i < nt * (DR_COLS / 4); i += DR_THREADS) {
-        const int tok = i / (DR_COLS / 4), c = (i - tok * (DR_COLS / 4)) * 4;
-        if (col0 + c < vdim)
-          dr_cp16(st + tok * TOK + 3 * DP + c, qkv + (long long)(t0 + tok) * C + 2 * n_kv * dim + h * vdim + col0 + c);
-      }
-      for (int tok = threadIdx.x; tok < nt; tok += DR_THREADS)
-        dr_cp4(st + tok * TOK + 3 * DP + DR_COLS, beta + (long long)(t0 + tok) * n_heads + h);
+      const int nt = min(DR_CHUNK, n - chunk * DR_CHUNK);
+#pragma unroll
+      for (int p = 0; p < NP; p++)
+        if (ptok[p] < nt) dr_cp16(st + dst[p], src[p] + (long long)chunk * pstep[p]);
+      if (vcopy && vtok < nt) dr_cp16(st + vtok * TOK + 3 * DP + vc, vsrc + (long long)chunk * DR_CHUNK * C);
+      if (bcopy && btok < nt) dr_cp4(st + btok * TOK + 3 * DP + DR_COLS, bsrc + (long long)chunk * DR_CHUNK * n_heads);
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
@@ -260,34 +280,35 @@ delta_recurrence_staged_kernel(const float* __restrict__ qkv, const float* __res
       const float4* k4 = reinterpret_cast<const float4*>(row + DP);
       const float4* g4 = reinterpret_cast<const float4*>(row + 2 * DP);
       const float v = row[3 * DP + ci], b = row[3 * DP + DR_COLS];
-      float dot0 = 0.f, dot1 = 0.f;
+      // a partial sum per group of four channels: independent chains
+      float4 kk[DPT / 4];
+      float dp[DPT / 4];
 #pragma unroll
       for (int i4 = 0; i4 < DPT / 4; i4++) {
-        const float4 g = g4[i4 * DR_LANES + part], k = k4[i4 * DR_LANES + part];
+        const float4 g = g4[i4 * DR_LANES + part];
+        kk[i4] = k4[i4 * DR_LANES + part];
         s[4 * i4] *= g.x; s[4 * i4 + 1] *= g.y; s[4 * i4 + 2] *= g.z; s[4 * i4 + 3] *= g.w;
-        dot0 = fmaf(s[4 * i4], k.x, dot0);
-        dot1 = fmaf(s[4 * i4 + 1], k.y, dot1);
-        dot0 = fmaf(s[4 * i4 + 2], k.z, dot0);
-        dot1 = fmaf(s[4 * i4 + 3], k.w, dot1);
+        dp[i4] = fmaf(s[4 * i4 + 3], kk[i4].w, fmaf(s[4 * i4 + 2], kk[i4].z, fmaf(s[4 * i4 + 1], kk[i4].y, s[4 * i4] * kk[i4].x)));
       }
-      float dot = dot0 + dot1;
+      float dot = dp[0];
+#pragma unroll
+      for (int i4 = 1; i4 < DPT / 4; i4++) dot += dp[i4];
 #pragma unroll
       for (int off = 1; off < DR_LANES; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
       const float u = b * (v - dot);
-      float o0 = 0.f, o1 = 0.f;
+      float op[DPT / 4];
 #pragma unroll
       for (int i4 = 0; i4 < DPT / 4; i4++) {
-        const float4 k = k4[i4 * DR_LANES + part], q = q4[i4 * DR_LANES + part];
-        s[4 * i4] = fmaf(k.x, u, s[4 * i4]);
-        s[4 * i4 + 1] = fmaf(k.y, u, s[4 * i4 + 1]);
-        s[4 * i4 + 2] = fmaf(k.z, u, s[4 * i4 + 2]);
-        s[4 * i4 + 3] = fmaf(k.w, u, s[4 * i4 + 3]);
-        o0 = fmaf(s[4 * i4], q.x, o0);
-        o1 = fmaf(s[4 * i4 + 1], q.y, o1);
-        o0 = fmaf(s[4 * i4 + 2], q.z, o0);
-        o1 = fmaf(s[4 * i4 + 3], q.w, o1);
+        const float4 q = q4[i4 * DR_LANES + part];
+        s[4 * i4] = fmaf(kk[i4].x, u, s[4 * i4]);
+        s[4 * i4 + 1] = fmaf(kk[i4].y, u, s[4 * i4 + 1]);
+        s[4 * i4 + 2] = fmaf(kk[i4].z, u, s[4 * i4 + 2]);
+        s[4 * i4 + 3] = fmaf(kk[i4].w, u, s[4 * i4 + 3]);
+        op[i4] = fmaf(s[4 * i4 + 3], q.w, fmaf(s[4 * i4 + 2], q.z, fmaf(s[4 * i4 + 1], q.y, s[4 * i4] * q.x)));
       }
-      float o = o0 + o1;
+      float o = op[0];
+#pragma unroll
+      for (int i4 = 1; i4 < DPT / 4; i4++) o += op[i4];
 #pragma unroll
       for (int off = 1; off < DR_LANES; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
       if (live && part == 0)
