@@ -29,7 +29,8 @@ from .loading import load_model, parse_dtype
 from .step import ModelRunner, StepEntry
 
 REPLAY_PAGE_SIZE = 16
-MAX_LIVE = 8
+MAX_LIVE = 8          # slots of a runner made by a caller that does not say
+TRACE_MAX_LIVE = 4    # slots of the command-line replayer: a trace never has more live requests
 
 
 def make_runner(model_dir: str, dtype, max_tokens: int, page_size: int = REPLAY_PAGE_SIZE,
@@ -79,7 +80,9 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+    ap.add_argument("--max-live", type=int, default=TRACE_MAX_LIVE,
+                    help="slots for per-request state: the most requests that are live at any time")
     args = ap.parse_args(argv)
-    runner = make_runner(args.model, args.dtype, args.max_tokens)
+    runner = make_runner(args.model, args.dtype, args.max_tokens, max_seqs=args.max_live)
     replay(runner, sys.stdin, args.out)
     return 0

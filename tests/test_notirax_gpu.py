@@ -533,3 +533,34 @@ def test_greedy_generation_through_the_engine(models, which):
     eng16 = mf.Engine(model_spec=d, dtype="bfloat16", kv_pool_tokens=1024, max_running=4)
     out16 = eng16.generate(prompts, max_tokens=6)
     assert all(len(o) == 6 for o in out16)
+
+
+def test_cli_generate_and_trace_run_for_notirax(models, tmp_path, capsys):
+    """The command line's own entry points: `generate` prints the plain implementation's greedy tokens, and the
+    replayer's program (four slots unless told otherwise) writes the logits of a small trace."""
+    from mlxforge_b200 import cli
+    from mlxforge_b200.engine import replay as R
+    d, cfg, reqs, expected, tols, w = models[("B", False)]
+    prompt_ids = reqs["r2"][:20]
+    capsys.readouterr()
+    assert cli.main(["generate", d, ",".join(map(str, prompt_ids)), "5", "--dtype", "float32"]) == 0
+    got = [int(t) for t in capsys.readouterr().out.split()]
+    seq, want = list(prompt_ids), []
+    for _ in range(5):
+        row = P.forward(cfg, w, seq)[-1]
+        want.append(int(np.argmax(row)))
+        seq.append(want[-1])
+    assert got == want, (got, want)
+    trace = TT.mixed(reqs, max_live=4, seed=1, decode_last=4)
+    out_dir = tmp_path / "out"
+    import sys
+    old = sys.stdin
+    sys.stdin = trace.lines()
+    try:
+        assert R.main(["--model", d, "--dtype", "float32", "--out", str(out_dir), "--max-tokens",
+                       str(trace.live_tokens_rounded())]) == 0
+    finally:
+        sys.stdin = old
+    capsys.readouterr()
+    worst, where = TT.worst(TT.read_outputs(trace, str(out_dir), cfg["vocab"]), expected)
+    assert worst <= tols["float32"], (worst, where)

@@ -276,3 +276,21 @@ def test_chunked_group_gives_pages_back_at_chunk_starts():
     assert seq.pages_held(0) < seq.pages_held(1)
     cm.close(seq)
     assert cm.free_pages() == cm.total_pages()
+
+
+# ----------------------------------------------------------------------------- command line without a device
+
+def test_cli_random_weights_and_dump_for_notirax(tmp_path, capsys):
+    from mlxforge_b200 import cli
+    from mlxforge_b200.config import config_from_json
+    from mlxforge_b200.weights.loader import tensor_shapes as file_shapes
+    cfg = config_from_json(json.loads(json.dumps(NX_A))).with_tensor_shapes(dict(tensor_shapes(NX_A, RANKS_A)))
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(cfg.to_json()))
+    out = tmp_path / "model"
+    assert cli.main(["random-weights", str(cfg_path), str(out), "--seed", "5"]) == 0
+    assert file_shapes(str(out)) == dict(tensor_shapes(NX_A, RANKS_A))
+    capsys.readouterr()
+    assert cli.main(["dump-weights", str(out)]) == 0
+    text = capsys.readouterr().out
+    assert "l0.mix.a1 [5, 48] BF16" in text and "l1.mix.talk [4, 4] BF16" in text and "l1.hc1.mix [2, 2] BF16" in text
