@@ -389,19 +389,24 @@ class KernelTimes:
         self.ops, self.names, self.calls, self.saved = ops, names, [], {}
 
     def __enter__(self):
+        import torch
         for n in self.names:
-            fn = getattr(self.ops, n)
-            self.saved[n] = fn
+            # the library's grouped product is not one of this engine's launchers but stands among them
+            owner = torch if n == "_grouped_mm" else self.ops
+            if not hasattr(owner, n):
+                continue
+            fn = getattr(owner, n)
+            self.saved[n] = (owner, fn)
 
             def rec(*a, _n=n, _fn=fn, **k):
                 self.calls.append((_n, _fn, a, k))
                 return _fn(*a, **k)
-            setattr(self.ops, n, rec)
+            setattr(owner, n, rec)
         return self
 
     def __exit__(self, *exc):
-        for n, fn in self.saved.items():
-            setattr(self.ops, n, fn)
+        for n, (owner, fn) in self.saved.items():
+            setattr(owner, n, fn)
 
     def measure(self, reps=7):
         import torch
@@ -465,6 +470,11 @@ def kernel_work(name, a, k, info):
     if name == "moe_grouped_down":
         w_down = a[1]
         return (0, 2.0 * a[5] * a[6] * w_down.shape[1] * w_down.shape[2], 0)
+    if name == "_grouped_mm":
+        x, w = a[0], a[1]
+        return (0, 2.0 * x.shape[0] * w.shape[1] * w.shape[2], 0)
+    if name in ("moe_gather_rows", "moe_activation"):
+        return (_nbytes(*[t for t in a if hasattr(t, "numel") and t.dim() >= 2]), 0, 0)
     if name == "moe_rows":
         x, w_gu, ids = a[0], a[1], a[3]
         return (ids.numel() * 3 * w_gu.shape[2] * x.shape[1] * 2, 0, 0)
@@ -476,7 +486,8 @@ def kernel_work(name, a, k, info):
 
 NOTIRAX_KERNELS = ("embed_positions", "hyper_update_norm", "biased_kv_store", "attention_talking", "attention_talking_tc",
                    "delta_prepare", "delta_gates", "delta_recurrence", "delta_output", "moe_route", "moe_rows",
-                   "moe_combine", "moe_sort", "moe_grouped_up", "moe_grouped_down", "stream_linear", "gemm_bf16")
+                   "moe_combine", "moe_sort", "moe_grouped_up", "moe_grouped_down", "moe_gather_rows", "moe_activation",
+                   "_grouped_mm", "stream_linear", "gemm_bf16")
 LLAMA_KERNELS = ("embed", "add_rmsnorm", "rope_kv_write", "attention_prefill", "attention_decode", "swiglu",
                  "stream_linear", "gemm_bf16")
 

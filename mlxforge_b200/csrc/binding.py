@@ -66,7 +66,9 @@ _SIGNATURES = {
     "mf_delta_output": [_P, _P, c_int, _P, c_float, _P, c_int, c_int, c_int, c_int, _P],
     "mf_moe_route": [_P, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P],
     "mf_moe_rows": [_P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float, c_float, _P],
-    "mf_moe_combine": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "mf_moe_combine": [_P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "mf_moe_gather_rows": [_P, _P, _P, c_int, c_int, _P],
+    "mf_moe_activation": [_P, _P, c_int, c_int, c_float, c_float, _P],
     "mf_moe_rows_slices": [c_int],
     "mf_attention_talking_tc_ok": [c_int, c_int, c_int, c_int, c_int],
     "mf_attention_talking_tc": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int,
@@ -74,7 +76,7 @@ _SIGNATURES = {
     "mf_attention_talking_splits": [c_int],
     "mf_attention_talking_decode": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int,
                                     c_float, c_float, _P, c_int, c_int, c_int, _P, _P, _P],
-    "mf_moe_sort": [_P, c_int, c_int, c_int, _P, _P, _P, _P, _P],
+    "mf_moe_sort": [_P, c_int, c_int, c_int, _P, _P, _P, _P, _P, _P],
     "mf_moe_grouped_ok": [c_int, c_int, c_int],
     "mf_moe_grouped_max_tiles": [c_int, c_int, c_int],
     "mf_moe_grouped_up": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P],

@@ -257,9 +257,9 @@ MF_API int mf_moe_rows(const void* x, const void* w_gu, const void* w_down, int 
 // out[t] = sum_k weights[t, k] * sum_s y[src(t, k) * slices + s], k in the order of the choice,
 // the slices of an expert in their order.  `slot_of` null: src(t, k) = t * top + k; else the row
 // of y that holds the pair (tokens sorted by expert).
-template <typename TO>
+template <typename TO, typename TY>
 __global__ void __launch_bounds__(256)
-moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, const int* __restrict__ slot_of,
+moe_combine_kernel(const TY* __restrict__ y, const float* __restrict__ weights, const int* __restrict__ slot_of,
                    TO* __restrict__ out, int H, int top, int slices) {
   pdl_launch();
   pdl_wait();
@@ -269,22 +269,24 @@ moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weight
     for (int k = 0; k < top; k++) {
       const long long row = (slot_of ? slot_of[(long long)t * top + k] : (long long)t * top + k) * slices;
       float part = 0.f;
-      for (int sl = 0; sl < slices; sl++) part += y[(row + sl) * H + i];
+      for (int sl = 0; sl < slices; sl++) part += to_f32<TY>(y[(row + sl) * H + i]);
       a = fmaf(weights[(long long)t * top + k], part, a);
     }
     out[(long long)t * H + i] = from_f32<TO>(a);
   }
 }
 
-MF_API int mf_moe_combine(const float* y, const float* weights, const int* slot_of, void* out, int out_dtype, int T,
-                          int H, int top, int slices, cudaStream_t stream) {
+MF_API int mf_moe_combine(const void* y, int y_dtype, const float* weights, const int* slot_of, void* out, int out_dtype,
+                          int T, int H, int top, int slices, cudaStream_t stream) {
   if (T <= 0) return 0;
   mf_count(MF_K_MOE_COMBINE);
-  if (out_dtype == MF_F32)
-    return (int)launch_dep(moe_combine_kernel<float>, dim3(T, (H + 255) / 256), dim3(256), 0, stream, y, weights, slot_of, (float*)out,
-                           H, top, slices);
-  if (out_dtype == MF_BF16)
-    return (int)launch_dep(moe_combine_kernel<__nv_bfloat16>, dim3(T, (H + 255) / 256), dim3(256), 0, stream, y, weights, slot_of,
-                           (__nv_bfloat16*)out, H, top, slices);
+  const dim3 grid(T, (H + 255) / 256);
+#define MC_LAUNCH(TO, TY)                                                                                       \
+  return (int)launch_dep(moe_combine_kernel<TO, TY>, grid, dim3(256), 0, stream, (const TY*)y, weights, slot_of, \
+                         (TO*)out, H, top, slices)
+  if (y_dtype == MF_F32 && out_dtype == MF_F32) MC_LAUNCH(float, float);
+  if (y_dtype == MF_F32 && out_dtype == MF_BF16) MC_LAUNCH(__nv_bfloat16, float);
+  if (y_dtype == MF_BF16 && out_dtype == MF_BF16) MC_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef MC_LAUNCH
   return MF_ERR_BAD_DTYPE;
 }

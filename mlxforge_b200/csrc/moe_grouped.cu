@@ -7,6 +7,11 @@
 //                   Which row a pair gets inside its expert's range is not fixed, and need not be:
 //                   every row is computed by itself, and the sum over a token's experts is taken in
 //                   the order of the choice by the combine kernel.
+//                   `ends` [E] (optional): the row at which every expert's range ends.
+//   mf_moe_gather_rows, mf_moe_activation   for the path through the library's grouped product
+//                   (the engine uses library products for its other many-row projections too): the
+//                   tokens' rows copied into the order of the rows, and the clamped activation of a
+//                   [rows, 2 ff] product (gate columns, then up columns).
 //   mf_moe_grouped_up    act[row] = g sigmoid(alpha g) (u + 1) with g, u the clamped gate and up
 //                   products of the row's token (gathered by row_token), bfloat16.
 //   mf_moe_grouped_down  y[row] = Wd_e act[row], 32-bit.
@@ -35,7 +40,7 @@ __device__ __forceinline__ void mg_mma(float (&c)[4], const uint32_t (&a)[4], ui
 // meta: [0] number of tiles; tiles: [max_tiles][3] = expert, first row, rows
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int top, int* __restrict__ slot_of,
-                int* __restrict__ row_token, int* __restrict__ meta, int* __restrict__ tiles) {
+                int* __restrict__ row_token, int* __restrict__ meta, int* __restrict__ tiles, int* __restrict__ ends) {
   __shared__ int count[MG_MAX_EXPERTS], offset[MG_MAX_EXPERTS], cursor[MG_MAX_EXPERTS];
   for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = cursor[e] = 0;
   __syncthreads();
@@ -52,6 +57,7 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int top, int* _
         nt++;
       }
       off += count[e];
+      if (ends) ends[e] = off;                 // where the expert's rows end: what a grouped library product reads
     }
     meta[0] = nt;
   }
@@ -65,14 +71,19 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int E, int top, int* _
 }
 
 MF_API int mf_moe_sort(const int* ids, int T, int E, int top, int* slot_of, int* row_token, int* meta, int* tiles,
-                       cudaStream_t stream) {
+                       int* ends, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E < 1 || E > MG_MAX_EXPERTS) return MF_ERR_BAD_ARG;
   mf_count(MF_K_MOE_SORT);
-  moe_sort_kernel<<<1, 1024, 0, stream>>>(ids, T * top, E, top, slot_of, row_token, meta, tiles);
+  moe_sort_kernel<<<1, 1024, 0, stream>>>(ids, T * top, E, top, slot_of, row_token, meta, tiles, ends);
   return (int)cudaGetLastError();
 }
 
+__device__ __forceinline__ void mg_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
 __device__ __forceinline__ void mg_cp16(void* smem, const void* gmem) {
   const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(addr), "l"(gmem) : "memory");
@@ -85,7 +96,6 @@ template <int NB, typename ARow, typename BRow>
 __device__ __forceinline__ void mg_tile(float (&acc)[NB][MG_BN / 8][4], int K, ARow arow, BRow brow,
                                         __nv_bfloat16* As, __nv_bfloat16* Bs) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int r0 = lane >> 2, c2 = (lane & 3) * 2;
   auto load = [&](int k0, int stage) {
     __nv_bfloat16* Ad = As + (size_t)stage * MG_BM * MG_LD;
     __nv_bfloat16* Bd = Bs + (size_t)stage * NB * MG_BN * MG_LD;
@@ -117,18 +127,17 @@ __device__ __forceinline__ void mg_tile(float (&acc)[NB][MG_BN / 8][4], int K, A
     const __nv_bfloat16* Bc = Bs + (size_t)stage * NB * MG_BN * MG_LD;
 #pragma unroll
     for (int kk = 0; kk < MG_BK; kk += 16) {
+      // fragments by ldmatrix: A's four 8x8 blocks in one load, B's blocks of two column tiles in one
       uint32_t af[4];
-      const __nv_bfloat16* ar = Ac + (warp * 16 + r0) * MG_LD + kk + c2;
-      af[0] = *reinterpret_cast<const uint32_t*>(ar);
-      af[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * MG_LD);
-      af[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
-      af[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * MG_LD + 8);
+      mg_ldmatrix_x4(af, Ac + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * MG_LD + kk + (lane >> 4) * 8);
 #pragma unroll
       for (int b = 0; b < NB; b++) {
 #pragma unroll
-        for (int nt = 0; nt < MG_BN / 8; nt++) {
-          const __nv_bfloat16* br = Bc + (b * MG_BN + nt * 8 + r0) * MG_LD + kk + c2;
-          mg_mma(acc[b][nt], af, *reinterpret_cast<const uint32_t*>(br), *reinterpret_cast<const uint32_t*>(br + 8));
+        for (int nt = 0; nt < MG_BN / 8; nt += 2) {
+          uint32_t bf[4];
+          mg_ldmatrix_x4(bf, Bc + (b * MG_BN + nt * 8 + (lane & 7) + (lane >> 4) * 8) * MG_LD + kk + ((lane >> 3) & 1) * 8);
+          mg_mma(acc[b][nt], af, bf[0], bf[1]);
+          mg_mma(acc[b][nt + 1], af, bf[2], bf[3]);
         }
       }
     }
@@ -250,5 +259,45 @@ MF_API int mf_moe_grouped_down(const void* act, const void* w_down, const int* m
   const size_t smem = (size_t)MG_STAGES * (MG_BM + MG_BN) * MG_LD * sizeof(__nv_bfloat16);
   moe_grouped_down_kernel<<<grid, 128, smem, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, meta, tiles,
                                                     y, H, ff);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ around the library's grouped product
+// xg[row] = x[row_token[row]], 16 bytes a copy (H a multiple of 8)
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ row_token, uint4* __restrict__ xg, int h8) {
+  const long long row = blockIdx.x;
+  const uint4* src = x + (long long)row_token[row] * h8;
+  for (int i = threadIdx.x; i < h8; i += blockDim.x) xg[row * h8 + i] = src[i];
+}
+
+MF_API int mf_moe_gather_rows(const void* x, const int* row_token, void* xg, int n_rows, int H, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (H % 8) return MF_ERR_BAD_ARG;
+  mf_count(MF_K_MOE_GROUPED);
+  moe_gather_rows_kernel<<<n_rows, 256, 0, stream>>>((const uint4*)x, row_token, (uint4*)xg, H / 8);
+  return (int)cudaGetLastError();
+}
+
+// act[r, f] = g sigmoid(alpha g) (u + 1), g = min(gu[r, f], limit), u = clamp(gu[r, ff + f], -limit, limit)
+__global__ void __launch_bounds__(256)
+moe_activation_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int ff, float limit,
+                      float alpha, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long r = i / ff;
+  const int f = (int)(i - r * ff);
+  const float g = fminf(__bfloat162float(gu[r * 2 * ff + f]), limit);
+  const float u = fminf(fmaxf(__bfloat162float(gu[r * 2 * ff + ff + f]), -limit), limit);
+  act[i] = __float2bfloat16_rn(g * (1.0f / (1.0f + __expf(-alpha * g))) * (u + 1.0f));
+}
+
+MF_API int mf_moe_activation(const void* gu, void* act, int n_rows, int ff, float limit, float alpha,
+                             cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const long long total = (long long)n_rows * ff;
+  mf_count(MF_K_MOE_GROUPED);
+  moe_activation_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)gu,
+                                                                             (__nv_bfloat16*)act, ff, limit, alpha, total);
   return (int)cudaGetLastError();
 }

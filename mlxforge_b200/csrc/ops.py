@@ -493,8 +493,8 @@ def moe_combine(y: torch.Tensor, weights: torch.Tensor, slot_of: Optional[torch.
                 slices: int = 1) -> None:
     _need_cuda(y, weights, slot_of, out)
     T, H = out.shape
-    check(library().mf_moe_combine(y.data_ptr(), weights.data_ptr(), _ptr(slot_of), out.data_ptr(), dtype_code(out),
-                                   T, H, weights.shape[1], slices, _stream()), "moe_combine")
+    check(library().mf_moe_combine(y.data_ptr(), dtype_code(y), weights.data_ptr(), _ptr(slot_of), out.data_ptr(),
+                                   dtype_code(out), T, H, weights.shape[1], slices, _stream()), "moe_combine")
 
 
 def attention_talking_tc_ok(n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int) -> bool:
@@ -556,15 +556,30 @@ def moe_grouped_max_tiles(T: int, top: int, n_experts: int) -> int:
 
 
 def moe_sort(ids: torch.Tensor, n_experts: int, slot_of: torch.Tensor, row_token: torch.Tensor, meta: torch.Tensor,
-             tiles: torch.Tensor) -> None:
+             tiles: torch.Tensor, ends: Optional[torch.Tensor] = None) -> None:
     """Order the (token, choice) pairs by expert: ``slot_of`` [T * top] the row of every pair, ``row_token``
-    the token of every row, ``meta[0]`` the number of tiles and ``tiles`` [n, 3] = expert, first row, rows."""
-    _need_cuda(ids, slot_of, row_token, meta, tiles)
+    the token of every row, ``meta[0]`` the number of tiles, ``tiles`` [n, 3] = expert, first row, rows, and
+    (if given) ``ends`` [n_experts] the row at which every expert's range ends."""
+    _need_cuda(ids, slot_of, row_token, meta, tiles, ends)
     T, top = ids.shape
     if tiles.numel() < 3 * moe_grouped_max_tiles(T, top, n_experts):
         raise KernelError("moe_sort: the tile list is too small")
     check(library().mf_moe_sort(ids.data_ptr(), T, n_experts, top, slot_of.data_ptr(), row_token.data_ptr(),
-                                meta.data_ptr(), tiles.data_ptr(), _stream()), "moe_sort")
+                                meta.data_ptr(), tiles.data_ptr(), _ptr(ends), _stream()), "moe_sort")
+
+
+def moe_gather_rows(x: torch.Tensor, row_token: torch.Tensor, xg: torch.Tensor) -> None:
+    """xg[row] = x[row_token[row]] (bfloat16 rows of a multiple of 8 columns)."""
+    _need_cuda(x, row_token, xg)
+    check(library().mf_moe_gather_rows(x.data_ptr(), row_token.data_ptr(), xg.data_ptr(), xg.shape[0], x.shape[1],
+                                       _stream()), "moe_gather_rows")
+
+
+def moe_activation(gu: torch.Tensor, act: torch.Tensor, limit: float, alpha: float) -> None:
+    """act [rows, ff] from a product gu [rows, 2 ff] (gate columns, then up columns): the clamped gated activation."""
+    _need_cuda(gu, act)
+    check(library().mf_moe_activation(gu.data_ptr(), act.data_ptr(), act.shape[0], act.shape[1], limit, alpha,
+                                      _stream()), "moe_activation")
 
 
 def moe_grouped_up(x: torch.Tensor, w_gu: torch.Tensor, row_token: torch.Tensor, meta: torch.Tensor,

@@ -11,11 +11,16 @@ ties go to the lower index.  Expert ``e``:
 The experts' matrices are stacked at load time (``[E, 2, ff, H]`` gate rows then up rows, and
 ``[E, H, ff]``).  Few tokens (and the 32-bit path) take the kernel with a block per (token, chosen
 expert), which streams that expert's matrices once; many tokens in bfloat16 are sorted by expert
-and go through tensor-core tiles.  Either way a token's chosen experts are added in the order of
-the choice, so its result does not depend on what else is in the batch.
+and go through the library's grouped product (as the engine's other many-row products go through
+the library) with this engine's gather, activation and weighted-sum kernels around it, or, where
+nothing may be allocated (a CUDA graph being recorded), the library lacks it, or the backend is
+``tcgen05``/``MLXFORGE_MOE_TILES=1``, through this engine's own tensor-core tiles.  Either way a
+token's chosen experts are added in the order of the choice, so its result does not depend on what
+else is in the batch.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict
 
 import torch
@@ -98,16 +103,32 @@ class RoutedExperts(FeedForward):
         ops.moe_combine(y, weights, None, out, slices)
         return out
 
+    def _library_grouped(self) -> bool:
+        """Whether the two products of the sorted pairs go through the library's grouped product."""
+        if os.environ.get("MLXFORGE_MOE_TILES", "0") == "1" or getattr(self.rt, "gemm_backend", "auto") == "tcgen05":
+            return False
+        return hasattr(torch, "_grouped_mm") and not torch.cuda.is_current_stream_capturing()
+
     def forward_grouped(self, x, ids, weights, out):
-        """Many tokens: pairs ordered by expert, tensor-core tiles, the weighted sum in the order of the choice."""
+        """Many tokens: pairs ordered by expert, the two products over the sorted rows, the weighted sum in
+        the order of the choice."""
         rt, T = self.rt, x.shape[0]
         i32, n = torch.int32, T * self.top
         slot_of = rt.buffer("moe.slot_of", (n,), i32)
         row_token = rt.buffer("moe.row_token", (n,), i32)
         meta = rt.buffer("moe.meta", (4,), i32)
         tiles = rt.buffer("moe.tiles", (3 * ops.moe_grouped_max_tiles(T, self.top, self.n_experts),), i32)
-        ops.moe_sort(ids, self.n_experts, slot_of, row_token, meta, tiles)
+        ends = rt.buffer("moe.ends", (self.n_experts,), i32)
+        ops.moe_sort(ids, self.n_experts, slot_of, row_token, meta, tiles, ends)
         act = rt.buffer("moe.act", (n, self.ff))
+        if self._library_grouped():
+            xg = rt.buffer("moe.xg", (n, self.hidden))
+            ops.moe_gather_rows(x, row_token, xg)
+            gu = torch._grouped_mm(xg, self.w_gu.view(self.n_experts, 2 * self.ff, self.hidden).transpose(1, 2), offs=ends)
+            ops.moe_activation(gu, act, self.limit, self.alpha)
+            y = torch._grouped_mm(act, self.w_down.transpose(1, 2), offs=ends)
+            ops.moe_combine(y, weights, slot_of, out)
+            return out
         ops.moe_grouped_up(x, self.w_gu, row_token, meta, tiles, act, self.top, self.limit, self.alpha)
         y = rt.buffer("moe.y", (n, self.hidden), torch.float32)
         ops.moe_grouped_down(act, self.w_down, meta, tiles, y, T, self.top)

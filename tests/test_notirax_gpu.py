@@ -384,11 +384,19 @@ def test_router_kernel(E, groups, keep, top):
         assert (np.sort(free, -1) != np.sort(chosen, -1)).any(-1).mean() > 0.1, "the groups never decide in this test"
 
 
+@pytest.mark.parametrize("own_tiles", [False, True])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,ff,E,groups,keep,top,T", [(40, 24, 6, 3, 2, 2, 9), (64, 64, 8, 0, 0, 3, 150),
                                                        (128, 32, 16, 4, 2, 4, 300), (72, 20, 5, 0, 0, 1, 70)])
-def test_routed_experts_part(dtype, H, ff, E, groups, keep, top, T):
+def test_routed_experts_part(dtype, H, ff, E, groups, keep, top, T, own_tiles, monkeypatch):
+    """``own_tiles``: many tokens in bfloat16 through this engine's own tensor-core tiles instead of the
+    library's grouped product (the other cases take the same kernels either way)."""
+    from mlxforge_b200.csrc import binding
     from mlxforge_b200.engine.runtime import Runtime
+    if own_tiles and (dtype != "bfloat16" or T < 64 or H % 8 or ff % 8):
+        pytest.skip("the path does not differ here")
+    monkeypatch.setenv("MLXFORGE_MOE_TILES", "1" if own_tiles else "0")
+    before = binding.kernel_launches()
     from mlxforge_b200.parts.base import FEED_FORWARDS, PartSpec, build_part
     rng = np.random.default_rng(H + T)
     params = {"hidden_size": H, "intermediate_size": ff, "n_experts": E, "top": top, "n_groups": groups,
@@ -407,6 +415,11 @@ def test_routed_experts_part(dtype, H, ff, E, groups, keep, top, T):
     # a token whose choice hangs on a close call may differ in bfloat16 (the router reads the same
     # bfloat16 inputs, so here it does not); all others must agree
     assert np.max(np.abs(got - want)) < tol(dtype, np.abs(want).max())
+    ran = {k: v - before[k] for k, v in binding.kernel_launches().items() if v - before[k]}
+    if dtype == "bfloat16" and T >= 64 and H % 8 == 0 and ff % 8 == 0:
+        assert ran.get("moe_grouped", 0) == (2 if own_tiles else 2) and ran.get("moe_sort", 0) == 1, ran
+    else:
+        assert ran.get("moe_rows", 0) == 1, ran
     # each token alone gives the same as inside the batch
     alone = host(part.forward(dev(x[7:8], tdt(dtype)), None))
     assert np.max(np.abs(alone[0] - got[7])) < (1e-5 if dtype == "float32" else 2e-2) * max(1.0, np.abs(want).max())
@@ -498,8 +511,11 @@ def test_every_request_decoded_from_its_first_token(models, which, dtype, tmp_pa
     _check(models, which, False, dtype, TT.lockstep(reqs), tmp_path, max_seqs=len(reqs))
 
 
-def test_serving_shapes_take_the_fast_kernels(models, tmp_path):
-    """Configuration C in bfloat16: which kernels its prompts and its decoding go through."""
+@pytest.mark.parametrize("own_tiles", [False, True])
+def test_serving_shapes_take_the_fast_kernels(models, tmp_path, own_tiles, monkeypatch):
+    """Configuration C in bfloat16: which kernels its prompts and its decoding go through, with the experts of
+    many tokens through the library's grouped product and through this engine's own tiles."""
+    monkeypatch.setenv("MLXFORGE_MOE_TILES", "1" if own_tiles else "0")
     reqs = models[("C", False)][2]
     ran = _check(models, "C", False, "bfloat16", TT.decode_tail(reqs, tail=8), tmp_path)
     for k in ("hyper_norm", "delta_recurrence", "moe_route", "embed_positions", "kv_store"):
