@@ -453,6 +453,9 @@ def kernel_work(name, a, k, info):
     if name == "attention_talking":
         n_kv, dim, vdim = a[9], a[10], a[11]
         return (ctx_keys * n_kv * (dim + vdim) * 2, 0, 0)
+    if name == "attention_talking_decode":
+        n_kv, dim, vdim = a[10], a[11], a[12]
+        return (ctx_keys * n_kv * (dim + vdim) * 2, 0, 0)
     if name == "attention_decode":
         n_kv, hd = a[11], a[12]
         return (ctx_keys * n_kv * 2 * hd * 2, 0, 0)
@@ -485,6 +488,7 @@ def kernel_work(name, a, k, info):
 
 
 NOTIRAX_KERNELS = ("embed_positions", "hyper_update_norm", "biased_kv_store", "attention_talking", "attention_talking_tc",
+                   "attention_talking_decode",
                    "delta_prepare", "delta_gates", "delta_recurrence", "delta_output", "moe_route", "moe_rows",
                    "moe_combine", "moe_sort", "moe_grouped_up", "moe_grouped_down", "moe_gather_rows", "moe_activation",
                    "_grouped_mm", "stream_linear", "gemm_bf16")
@@ -512,8 +516,9 @@ def kernel_table(engine, names, tokens, batch, ctx, chunk, pk):
             runner.step(entries)
             torch.cuda.synchronize()
         for n, calls in kt.measure().items():
-            us = statistics.median(c[0] for c in calls)
-            b, tf, ff = kernel_work(n, calls[0][1], calls[0][2], info)
+            # the call whose time is the median of its kind stands for the kind, with its own work
+            us, a, k = sorted(calls, key=lambda c: c[0])[len(calls) // 2]
+            b, tf, ff = kernel_work(n, a, k, info)
             roof = max(b / (pk["hbm_gbs"] * 1e9), tf / (pk["bf16_tflops"] * 1e12), ff / (FP32_TFLOPS_NOMINAL * 1e12)) * 1e6
             table[f"{phase}.{n}"] = {"us": round(us, 1), "calls": len(calls), "roof_us": round(roof, 2),
                                      "frac": round(roof / us, 3) if roof else None,

@@ -19,7 +19,10 @@
 // Decoding (one query per sequence) runs the same kernel with the keys cut into splits of
 // TT_SPLIT_TILES tiles that start at multiples of that many tiles: a block per (sequence, split)
 // writes its unnormalised output with its running maximum and sum, and a merge kernel joins the
-// splits.  A split's range depends on positions only.
+// splits.  A split's range depends on positions only.  Portions of prompts whose queries see more
+// than TT_PREFILL_SPLIT_TILES tiles of keys are cut the same way (the last tile of queries of a
+// long prompt would otherwise walk all its keys alone while the blocks of the first tiles are
+// long done).
 //
 // Steps 1 and 3 are tensor-core work of 2 * 16 * 32 * (dim + vdim) MACs per head; step 2 is
 // H^2 * 512 32-bit FMAs per tile plus a tanh and an exponential per score, which is what bounds
@@ -30,6 +33,7 @@
 #define TT_BN 32
 #define TT_SPAD 4          // floats of padding per row of the score tile
 #define TT_SPLIT_TILES 4   // key tiles per split when decoding (128 keys)
+#define TT_PREFILL_SPLIT_TILES 32   // and for portions of prompts (1024 keys)
 
 __device__ __forceinline__ void tt_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -71,7 +75,8 @@ struct TtArgs {
   int table_row0, bt_stride, page_size, n_heads, n_kv, dim;
   float scale, softcap;
   int window, chunk;
-  int splits;               // 0: every block walks all its keys; else gridDim.z splits of TT_SPLIT_TILES tiles
+  int splits;               // 0: every block walks all its keys; else gridDim.z splits of split_tiles tiles
+  int split_tiles;
   float* part_o;            // [rows, splits, H, VDIM] unnormalised outputs of the splits
   float* part_ml;           // [rows, splits, H, 2]    running maximum and sum
 };
@@ -138,7 +143,7 @@ talking_attention_tc_kernel(const TtArgs a) {
   }
   int k_first = (lo0 / TT_BN) * TT_BN, k_last = pos_last;
   if (a.splits > 0) {      // this block's share: tiles [z, z + 1) * TT_SPLIT_TILES of the sequence
-    const int span = TT_SPLIT_TILES * TT_BN;
+    const int span = a.split_tiles * TT_BN;
     const int first_split = k_first / span;
     k_first = max(k_first, (first_split + (int)blockIdx.z) * span);
     k_last = min(k_last, (first_split + (int)blockIdx.z + 1) * span - 1);
@@ -332,15 +337,20 @@ talking_attention_tc_kernel(const TtArgs a) {
       l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 1);
       l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 2);
     }
-    if (a.splits > 0) {      // one query per sequence: row 0, held by the first four lanes
-      if (r0 == 0) {
-        const long long slot = ((long long)(q_start + row0) * a.splits + blockIdx.z) * H + warp;
+    if (a.splits > 0) {      // the split's unnormalised rows with their maximum and sum
 #pragma unroll
-        for (int nt = 0; nt < VDIM / 8; nt++)
-          *reinterpret_cast<float2*>(a.part_o + slot * VDIM + nt * 8 + c2) = make_float2(o[nt][0], o[nt][1]);
-        if (c2 == 0) {
-          a.part_ml[slot * 2] = m_run[0];
-          a.part_ml[slot * 2 + 1] = l_run[0];
+      for (int half = 0; half < 2; half++) {
+        const int r = r0 + 8 * half;
+        if (r < rows) {
+          const long long slot = ((long long)(q_start + row0 + r) * a.splits + blockIdx.z) * H + warp;
+#pragma unroll
+          for (int nt = 0; nt < VDIM / 8; nt++)
+            *reinterpret_cast<float2*>(a.part_o + slot * VDIM + nt * 8 + c2) =
+                make_float2(o[nt][2 * half], o[nt][2 * half + 1]);
+          if (c2 == 0) {
+            a.part_ml[slot * 2] = m_run[half];
+            a.part_ml[slot * 2 + 1] = l_run[half];
+          }
         }
       }
       return;
@@ -375,8 +385,8 @@ MF_API int mf_attention_talking_tc_ok(int n_heads, int n_kv, int dim, int vdim, 
 // out[t, h] = sum_z o_z e^{m_z - m} / sum_z l_z e^{m_z - m}, the splits in their order
 __global__ void __launch_bounds__(128)
 talking_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                               __nv_bfloat16* __restrict__ out, int splits, int H, int vdim) {
-  const int t = blockIdx.x, h = blockIdx.y;
+                               __nv_bfloat16* __restrict__ out, int splits, int H, int vdim, int first_row) {
+  const int t = first_row + blockIdx.x, h = blockIdx.y;
   const float* ml = part_ml + ((long long)t * splits * H + h) * 2;
   float m = -INFINITY;
   for (int z = 0; z < splits; z++) m = fmaxf(m, ml[(long long)z * H * 2]);
@@ -420,24 +430,37 @@ MF_API int mf_attention_talking_tc(const void* q, const void* k_pool, const void
                                    const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
                                    int table_row0, int n_seqs, int max_q_len, int n_heads, int n_kv, int dim, int vdim,
                                    const int* block_table, int bt_stride, int page_size, float scale, float softcap,
-                                   const float* talk, int window, int chunk, cudaStream_t stream) {
+                                   const float* talk, int window, int chunk, int splits, float* part_o, float* part_ml,
+                                   int first_row, int n_rows, cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
-  if (!mf_attention_talking_tc_ok(n_heads, n_kv, dim, vdim, page_size) || n_seqs > 65535) return MF_ERR_BAD_ARG;
+  if (!mf_attention_talking_tc_ok(n_heads, n_kv, dim, vdim, page_size) || n_seqs > 65535 || splits < 0 || splits > 65535)
+    return MF_ERR_BAD_ARG;
   TtArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out,
            seq_q_start, seq_q_len, seq_ctx_len, block_table, talk, table_row0, bt_stride, page_size, n_heads, n_kv, dim,
-           scale, softcap, window, chunk, 0, nullptr, nullptr};
+           scale, softcap, window, chunk, splits, TT_PREFILL_SPLIT_TILES, part_o, part_ml};
   mf_count(MF_K_ATTN_TALKING_TC);
-#define TT_CASE(VD)                                                              \
-  if (vdim == VD) {                                                              \
-    if (n_heads <= 8) return tt_launch<VD, 8>(a, n_seqs, max_q_len, stream);     \
-    return tt_launch<VD, 16>(a, n_seqs, max_q_len, stream);                      \
-  }
+  int rc = MF_ERR_BAD_ARG;
+#define TT_CASE(VD)                                                         \
+  if (vdim == VD)                                                           \
+    rc = n_heads <= 8 ? tt_launch<VD, 8>(a, n_seqs, max_q_len, stream) : tt_launch<VD, 16>(a, n_seqs, max_q_len, stream);
   TT_CASE(32)
   TT_CASE(64)
   TT_CASE(96)
   TT_CASE(128)
 #undef TT_CASE
-  return MF_ERR_BAD_ARG;
+  if (rc != 0 || splits == 0) return rc;
+  // the rows of the portions are rows first_row .. first_row + n_rows of the step
+  mf_count(MF_K_ATTN_TALKING_MERGE);
+  talking_attention_merge_kernel<<<dim3(n_rows, n_heads), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, splits,
+                                                                        n_heads, vdim, first_row);
+  return (int)cudaGetLastError();
+}
+
+// Splits of a launch for portions of prompts whose queries see at most `max_keys` keys (0: none needed).
+MF_API int mf_attention_talking_prefill_splits(int max_keys) {
+  const int tiles = (max_keys + TT_BN - 1) / TT_BN + 1;
+  if (tiles <= TT_PREFILL_SPLIT_TILES + 1) return 0;
+  return (tiles + TT_PREFILL_SPLIT_TILES - 1) / TT_PREFILL_SPLIT_TILES + 1;
 }
 
 // Splits that a decode launch needs when no query sees more than `max_keys` keys.
@@ -459,7 +482,7 @@ MF_API int mf_attention_talking_decode(const void* q, const void* k_pool, const 
     return MF_ERR_BAD_ARG;
   TtArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out,
            seq_q_start, seq_q_len, seq_ctx_len, block_table, talk, 0, bt_stride, page_size, n_heads, n_kv, dim,
-           scale, softcap, window, chunk, splits, part_o, part_ml};
+           scale, softcap, window, chunk, splits, TT_SPLIT_TILES, part_o, part_ml};
   mf_count(MF_K_ATTN_TALKING_TC);
   int rc = MF_ERR_BAD_ARG;
 #define TT_CASE(VD)                                                         \
@@ -472,6 +495,6 @@ MF_API int mf_attention_talking_decode(const void* q, const void* k_pool, const 
   if (rc != 0) return rc;
   mf_count(MF_K_ATTN_TALKING_MERGE);
   talking_attention_merge_kernel<<<dim3(n_seqs, n_heads), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, splits,
-                                                                         n_heads, vdim);
+                                                                         n_heads, vdim, 0);
   return (int)cudaGetLastError();
 }

@@ -72,7 +72,8 @@ _SIGNATURES = {
     "mf_moe_rows_slices": [c_int],
     "mf_attention_talking_tc_ok": [c_int, c_int, c_int, c_int, c_int],
     "mf_attention_talking_tc": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int,
-                                c_int, c_float, c_float, _P, c_int, c_int, _P],
+                                c_int, c_float, c_float, _P, c_int, c_int, c_int, _P, _P, c_int, c_int, _P],
+    "mf_attention_talking_prefill_splits": [c_int],
     "mf_attention_talking_splits": [c_int],
     "mf_attention_talking_decode": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int,
                                     c_float, c_float, _P, c_int, c_int, c_int, _P, _P, _P],

@@ -506,18 +506,32 @@ def attention_talking_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                          seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, seq_ctx_len: torch.Tensor,
                          table_row0: int, max_q_len: int, block_table: torch.Tensor, page_size: int, n_heads: int,
                          n_kv: int, dim: int, vdim: int, scale: float, softcap: float, talk: Optional[torch.Tensor],
-                         window: int, chunk: int) -> None:
+                         window: int, chunk: int, splits: int = 0, part_o: Optional[torch.Tensor] = None,
+                         part_ml: Optional[torch.Tensor] = None, first_row: int = 0) -> None:
     """Talking-heads attention of prompt portions, bfloat16, on the tensor cores.  ``q`` / ``out`` are the
     whole step's rows; the three per-sequence arrays describe the sequences that start at row
-    ``table_row0`` of ``block_table``."""
-    _need_cuda(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, block_table, talk)
+    ``table_row0`` of ``block_table``.  ``splits`` > 0 (from ``attention_talking_prefill_splits``): long key
+    ranges are cut across blocks and merged; the scratch holds ``T * splits * n_heads * (vdim | 2)`` floats
+    and the portions are the step's rows from ``first_row`` on."""
+    _need_cuda(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, block_table, talk, part_o, part_ml)
     if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
         raise KernelError("attention_talking_tc: bfloat16 only")
+    T = q.shape[0]
+    if splits and (part_o is None or part_ml is None or part_o.numel() < T * splits * n_heads * vdim
+                   or part_ml.numel() < T * splits * n_heads * 2):
+        raise KernelError("attention_talking_tc: scratch for the splits is missing or too small")
     check(library().mf_attention_talking_tc(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
                                             seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_ctx_len.data_ptr(),
                                             table_row0, seq_q_len.shape[0], max_q_len, n_heads, n_kv, dim, vdim,
                                             block_table.data_ptr(), block_table.shape[1], page_size, scale, softcap,
-                                            _ptr(talk), window, chunk, _stream()), "attention_talking_tc")
+                                            _ptr(talk), window, chunk, splits, _ptr(part_o), _ptr(part_ml), first_row,
+                                            T - first_row, _stream()), "attention_talking_tc",
+          launches=2 if splits else 1)
+
+
+def attention_talking_prefill_splits(max_keys: int) -> int:
+    """Splits for portions of prompts whose queries see at most ``max_keys`` keys (0: not worth cutting)."""
+    return int(library().mf_attention_talking_prefill_splits(max_keys))
 
 
 def attention_talking_splits(max_keys: int) -> int:

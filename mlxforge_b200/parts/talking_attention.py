@@ -122,12 +122,12 @@ def talking_paged_attention(rt, batch, q, lane, out, m: TalkingAttention) -> Non
                               m.n_heads, m.n_kv, m.dim, m.vdim, m.scale, m.softcap, m.talk, m.window, m.chunk)
         return
     nd = batch.n_decode
+    max_keys = batch.max_ctx
+    if m.chunk:
+        max_keys = min(max_keys, m.chunk)
+    if m.window:
+        max_keys = min(max_keys, m.window)
     if nd > 0:
-        max_keys = batch.max_ctx
-        if m.chunk:
-            max_keys = min(max_keys, m.chunk)
-        if m.window:
-            max_keys = min(max_keys, m.window)
         splits = ops.attention_talking_splits(max_keys)
         part_o = rt.buffer("tattn.part_o", (nd * splits * m.n_heads * m.vdim,), torch.float32)
         part_ml = rt.buffer("tattn.part_ml", (nd * splits * m.n_heads * 2,), torch.float32)
@@ -135,6 +135,13 @@ def talking_paged_attention(rt, batch, q, lane, out, m: TalkingAttention) -> Non
                                      batch.seq_ctx_len[:nd], table, lane.page_size, m.n_heads, m.n_kv, m.dim, m.vdim,
                                      m.scale, m.softcap, m.talk, m.window, m.chunk, splits, part_o, part_ml)
     if nd < batch.n_tokens:
+        T = batch.n_tokens
+        splits = ops.attention_talking_prefill_splits(max_keys)
+        part_o = part_ml = None
+        if splits:
+            part_o = rt.buffer("tattn.part_o", (T * splits * m.n_heads * m.vdim,), torch.float32)
+            part_ml = rt.buffer("tattn.part_ml", (T * splits * m.n_heads * 2,), torch.float32)
         ops.attention_talking_tc(q, lane.k, lane.v, out, batch.seq_q_start[nd:], batch.seq_q_len[nd:],
                                  batch.seq_ctx_len[nd:], nd, max(batch.q_len[nd:]), table, lane.page_size,
-                                 m.n_heads, m.n_kv, m.dim, m.vdim, m.scale, m.softcap, m.talk, m.window, m.chunk)
+                                 m.n_heads, m.n_kv, m.dim, m.vdim, m.scale, m.softcap, m.talk, m.window, m.chunk,
+                                 splits, part_o, part_ml, nd)

@@ -50,7 +50,7 @@ def rand(rng, *shape, std=1.0):
 class Harness:
     """A runtime, a cache with one lane of the given need and the runner's metadata builder."""
 
-    def __init__(self, dtype, need, lengths=LENGTHS, steps=STEPS, page_size=16):
+    def __init__(self, dtype, need, lengths=LENGTHS, steps=STEPS, page_size=16, max_tokens=512):
         import torch
         from mlxforge_b200.cache.manager import CacheLayout, CacheManager, GroupLayout
         from mlxforge_b200.engine.runtime import Runtime
@@ -60,7 +60,8 @@ class Harness:
         paged = isinstance(need, PagedKV)
         layout = CacheLayout(paged=(GroupLayout(need, 1),) if paged else (), state=() if paged else (GroupLayout(need, 1),),
                              item_lane=(("paged" if paged else "state", 0, 0),))
-        self.cache = CacheManager(layout, page_size=page_size, max_tokens=512, max_seqs=4, dtype=tdt(dtype), device="cuda")
+        self.cache = CacheManager(layout, page_size=page_size, max_tokens=max_tokens, max_seqs=4, dtype=tdt(dtype),
+                                  device="cuda")
         for pool in self.cache._k + self.cache._v:
             pool.fill_(float("nan"))
         self.cache.open_sequence()                                     # so that the sequences do not sit in slot 0
@@ -178,7 +179,10 @@ ATTN_CASES = {
     "no_talk_no_chunk": (3, 1, 32, 8, 0, 0, 30.0, False),
     "window": (4, 2, 16, 24, 0, 9, 0.0, True),
     "tiles": (4, 2, 64, 64, 40, 0, 10.0, True),
+    "long": (4, 2, 64, 32, 0, 0, 10.0, True),        # no chunk and 1,300 tokens: the key range is cut across blocks
 }
+ATTN_PLANS = {"tiles": ([150, 70], [(129, 0), (2, 40), (18, 29), (1, 1)]),
+              "long": ([1300, 70], [(1100, 0), (150, 40), (49, 29), (1, 1)])}
 
 
 def _attention_part(dtype, case, rng, H=56, gain=1.0):
@@ -220,10 +224,10 @@ def test_talking_attention_part(dtype, case):
     from mlxforge_b200.parts.base import MIXERS, PartSpec, build_part
     rng = np.random.default_rng(sum(map(ord, case)))
     params, w, p, window = _attention_part(dtype, case, rng)
-    lengths, steps = (LENGTHS, STEPS) if case != "tiles" else ([150, 70], [(129, 0), (2, 40), (18, 29), (1, 1)])
+    lengths, steps = ATTN_PLANS.get(case, (LENGTHS, STEPS))
     part = build_part(MIXERS, PartSpec("talking_attention", params, prefix="a."), None)
     need = part.cache_need()
-    h = Harness(dtype, need, lengths, steps)
+    h = Harness(dtype, need, lengths, steps, max_tokens=2048)
     part = build_part(MIXERS, PartSpec("talking_attention", params, prefix="a."), h.rt)
     part.bind({n: dev(a) for n, a in w.items()})
     xs = [rand(rng, n, params["hidden_size"]) for n in lengths]
