@@ -276,10 +276,43 @@ moe_combine_kernel(const TY* __restrict__ y, const float* __restrict__ weights, 
   }
 }
 
+// bfloat16 rows in 16-byte pieces (H a multiple of 8, one partial sum per pair): 8 columns a thread
+__global__ void __launch_bounds__(256)
+moe_combine_bf16_vec_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ weights,
+                            const int* __restrict__ slot_of, __nv_bfloat16* __restrict__ out, int H, int top) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= H) return;
+  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int k = 0; k < top; k++) {
+    const long long row = slot_of ? slot_of[(long long)t * top + k] : (long long)t * top + k;
+    const float wk = weights[(long long)t * top + k];
+    const uint4 v = *reinterpret_cast<const uint4*>(y + row * H + i);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float2 f = __bfloat1622float2(p[j]);
+      a[2 * j] = fmaf(wk, f.x, a[2 * j]);
+      a[2 * j + 1] = fmaf(wk, f.y, a[2 * j + 1]);
+    }
+  }
+  uint4 o;
+  __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; j++) q[j] = __floats2bfloat162_rn(a[2 * j], a[2 * j + 1]);
+  *reinterpret_cast<uint4*>(out + (long long)t * H + i) = o;
+}
+
 MF_API int mf_moe_combine(const void* y, int y_dtype, const float* weights, const int* slot_of, void* out, int out_dtype,
                           int T, int H, int top, int slices, cudaStream_t stream) {
   if (T <= 0) return 0;
   mf_count(MF_K_MOE_COMBINE);
+  if (y_dtype == MF_BF16 && out_dtype == MF_BF16 && slices == 1 && H % 8 == 0 && ((uintptr_t)y & 15) == 0 &&
+      ((uintptr_t)out & 15) == 0)
+    return (int)launch_dep(moe_combine_bf16_vec_kernel, dim3(T, (H / 8 + 255) / 256), dim3(256), 0, stream,
+                           (const __nv_bfloat16*)y, weights, slot_of, (__nv_bfloat16*)out, H, top);
   const dim3 grid(T, (H + 255) / 256);
 #define MC_LAUNCH(TO, TY)                                                                                       \
   return (int)launch_dep(moe_combine_kernel<TO, TY>, grid, dim3(256), 0, stream, (const TY*)y, weights, slot_of, \

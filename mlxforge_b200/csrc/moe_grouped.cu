@@ -292,11 +292,43 @@ moe_activation_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __res
   act[i] = __float2bfloat16_rn(g * (1.0f / (1.0f + __expf(-alpha * g))) * (u + 1.0f));
 }
 
+// the same, 8 columns a thread (ff a multiple of 8)
+__global__ void __launch_bounds__(256)
+moe_activation_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int ff, float limit,
+                          float alpha, long long total8) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total8) return;
+  const int f8 = ff / 8;
+  const long long r = i / f8;
+  const int f = (int)(i - r * f8) * 8;
+  const uint4 gv = *reinterpret_cast<const uint4*>(gu + r * 2 * ff + f);
+  const uint4 uv = *reinterpret_cast<const uint4*>(gu + r * 2 * ff + ff + f);
+  const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+  const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uv);
+  uint4 o;
+  __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const float2 g2 = __bfloat1622float2(gp[j]), u2 = __bfloat1622float2(up[j]);
+    const float g0 = fminf(g2.x, limit), g1 = fminf(g2.y, limit);
+    const float u0 = fminf(fmaxf(u2.x, -limit), limit), u1 = fminf(fmaxf(u2.y, -limit), limit);
+    op[j] = __floats2bfloat162_rn(g0 * (1.0f / (1.0f + __expf(-alpha * g0))) * (u0 + 1.0f),
+                                  g1 * (1.0f / (1.0f + __expf(-alpha * g1))) * (u1 + 1.0f));
+  }
+  *reinterpret_cast<uint4*>(act + r * ff + f) = o;
+}
+
 MF_API int mf_moe_activation(const void* gu, void* act, int n_rows, int ff, float limit, float alpha,
                              cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   const long long total = (long long)n_rows * ff;
   mf_count(MF_K_MOE_GROUPED);
+  if (ff % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)act & 15) == 0) {
+    const long long total8 = total / 8;
+    moe_activation_vec_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, stream>>>(
+        (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, ff, limit, alpha, total8);
+    return (int)cudaGetLastError();
+  }
   moe_activation_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)gu,
                                                                              (__nv_bfloat16*)act, ff, limit, alpha, total);
   return (int)cudaGetLastError();
