@@ -180,6 +180,8 @@ ATTN_CASES = {
     "window": (4, 2, 16, 24, 0, 9, 0.0, True),
     "tiles": (4, 2, 64, 64, 40, 0, 10.0, True),
     "long": (4, 2, 64, 32, 0, 0, 10.0, True),        # no chunk and 1,300 tokens: the key range is cut across blocks
+    "two_heads": (2, 1, 32, 32, 24, 0, 5.0, True),   # fewer heads than the tensor-core kernel has warps
+    "sixteen_heads": (16, 4, 16, 96, 50, 0, 8.0, True),
 }
 ATTN_PLANS = {"tiles": ([150, 70], [(129, 0), (2, 40), (18, 29), (1, 1)]),
               "long": ([1300, 70], [(1100, 0), (150, 40), (49, 29), (1, 1)])}
@@ -282,6 +284,7 @@ DELTA_CASES = {
     "one_tap": (2, 2, 16, 16, 1, 4, 4),
     "wide": (2, 1, 128, 48, 2, 8, 8),
     "long_taps": (3, 3, 40, 24, 6, 2, 7),
+    "unaligned": (2, 1, 18, 10, 3, 3, 3),            # sizes that are no multiple of 4: the kernel without 16-byte copies
 }
 
 
