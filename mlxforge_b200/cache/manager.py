@@ -14,7 +14,8 @@ Pool layout of a paged lane: ``[page][kv_head][slot][head_dim]`` for keys and th
 same for values, so one head's page is contiguous.
 
 Pages are given back when a request is closed and, in a windowed group, as soon
-as every position of a page is older than the window of the next query; in a group
+as every position of a page is older than the window of the next query (pages of the
+first ``keep_first`` positions stay, where a group keeps them visible); in a group
 whose queries only see their own chunk, as soon as the next query's chunk starts
 behind the page.
 """
@@ -48,8 +49,8 @@ class CacheLayout:
     def bytes_per_token(self, elt_bytes: int) -> int:
         """Key+value bytes one token adds over all paged lanes
         (the reference's arithmetic: src/cache/kv_budget.cpp:50-60)."""
-        return sum(g.n_lanes * g.need.n_kv_heads * (g.need.head_dim + g.need.value_dim) * elt_bytes
-                   for g in self.paged)
+        return sum(g.n_lanes * g.need.n_kv_heads * elt_bytes
+                   * (g.need.head_dim + (0 if g.need.values_in_keys else g.need.value_dim)) for g in self.paged)
 
     def bytes_per_request(self) -> int:
         total = 0
@@ -116,7 +117,9 @@ class CacheManager:
         for g in layout.paged:
             shape = (g.n_lanes, self.n_pages, g.need.n_kv_heads, page_size)
             self._k.append(torch.zeros(shape + (g.need.head_dim,), dtype=dtype, device=device))
-            self._v.append(torch.zeros(shape + (g.need.value_dim,), dtype=dtype, device=device))
+            # values that are channels of the keys have no pool of their own: the lane's v is its k
+            self._v.append(self._k[-1] if g.need.values_in_keys
+                           else torch.zeros(shape + (g.need.value_dim,), dtype=dtype, device=device))
         self._state = [torch.zeros((g.n_lanes, max_seqs) + tuple(g.need.shape),
                                    dtype=getattr(torch, getattr(g.need, "dtype", "float32")), device=device)
                        for g in layout.state]
@@ -188,11 +191,15 @@ class CacheManager:
         for g in range(len(self.pools)):
             first = self._first_needed_block(g, seq.length)
             blocks = seq.blocks[g]
-            gone = [blocks[b] for b in range(min(first, len(blocks))) if blocks[b] >= 0]
+            # the blocks of positions that stay visible beside the window are never given back
+            kept = (self.layout.paged[g].need.keep_first + self.page_size - 1) // self.page_size
+            passed = range(min(kept, len(blocks)), min(first, len(blocks)))
+            gone = [blocks[b] for b in passed if blocks[b] >= 0]
             if gone:
-                for b in range(min(first, len(blocks))):
+                for b in passed:
                     blocks[b] = -1
-                seq.block_rows[g][:min(first, len(blocks))] = -1
+                if len(passed):
+                    seq.block_rows[g][passed.start:passed.stop] = -1
                 self.pools[g].give_back(gone)
 
     def close(self, seq: SequenceCache) -> None:

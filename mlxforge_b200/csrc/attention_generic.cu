@@ -12,13 +12,24 @@
 #include "common.cuh"
 
 #define CHUNK 128
+#define MAX_ACC 4      // value channels per thread: values up to MAX_ACC * CHUNK wide
 
+// Further options, all off at their defaults:
+//  * keys and values of unlike width: a key row is pv.head_dim wide, a value row `vd`, and value
+//    rows lie `v_ld` apart in their pool.  With v_pool == k_pool and v_ld == pv.head_dim the values
+//    are the first `vd` channels of the keys (one latent per token that is key and value at once);
+//  * keep_first > 0 (with a window): keys at positions below keep_first stay visible to every
+//    later query, at their own positions;
+//  * sink (one float per query head): exp(sink_h) joins the softmax denominator; it has no key
+//    and no value and is not scaled;
+//  * gate ([T, gate_ld], head h at column h * vd): the output is multiplied by sigmoid(gate).
 template <typename T>
 __global__ void __launch_bounds__(CHUNK)
 attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                          T* __restrict__ out, const int* __restrict__ positions,
                          const int* __restrict__ seq_of_token, PagedView pv, int n_heads, float scale,
-                         int window) {
+                         int window, int vd, int v_ld, int keep_first, const float* __restrict__ sink,
+                         const T* __restrict__ gate, int gate_ld) {
   extern __shared__ float smem[];
   float* qs = smem;                 // [hd]
   float* ps = smem + pv.head_dim;   // [CHUNK]
@@ -28,17 +39,30 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
   const int kvh = h / (n_heads / pv.n_kv_heads);
   const int pos = positions[t], seq = seq_of_token[t];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int keep = (window > 0 && keep_first > 0) ? min(keep_first, lo) : 0;   // kept keys before the window
 
   const T* qrow = q + ((long long)t * n_heads + h) * hd;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) qs[d] = to_f32<T>(qrow[d]);
   __syncthreads();
 
   float m = -INFINITY, l = 0.f;
-  float acc0 = 0.f, acc1 = 0.f;     // output channels threadIdx.x and threadIdx.x + CHUNK (hd <= 256)
-  for (int c0 = (lo / CHUNK) * CHUNK; c0 <= pos; c0 += CHUNK) {
+  if (sink) {                       // the sink as a key of score sink_h whose value is zero
+    m = sink[h];
+    l = 1.f;
+  }
+  float acc[MAX_ACC];
+#pragma unroll
+  for (int a = 0; a < MAX_ACC; a++) acc[a] = 0.f;
+  const int first_win = (lo / CHUNK) * CHUNK;
+  // the chunks of kept keys that lie wholly before the window's first chunk, then the window's
+  for (int c0 = (keep > 0 ? 0 : first_win); c0 <= pos; c0 += CHUNK) {
+    if (c0 < first_win && c0 >= keep) {
+      c0 = first_win - CHUNK;
+      continue;
+    }
     const int j = c0 + threadIdx.x;
     float s = -INFINITY;
-    if (j >= lo && j <= pos) {
+    if (j <= pos && (j >= lo || j < keep)) {
       const T* kr = k_pool + paged_offset(pv, seq, j, kvh);
       float dot = 0.f;
       for (int d = 0; d < hd; d++) dot = fmaf(qs[d], to_f32<T>(kr[d]), dot);
@@ -53,30 +77,43 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
     const float psum = block_sum(p, red);   // has __syncthreads inside: ps is visible after it
     l = l * alpha + psum;
     m = m_new;
-    acc0 *= alpha;
-    acc1 *= alpha;
+#pragma unroll
+    for (int a = 0; a < MAX_ACC; a++) acc[a] *= alpha;
     const int jn = min(CHUNK, pos - c0 + 1);
-    for (int jj = max(0, lo - c0); jj < jn; jj++) {
+    for (int jj = 0; jj < jn; jj++) {
+      const int key = c0 + jj;
+      if (key < lo && key >= keep) continue;
       const float pj = ps[jj];
-      const T* vr = v_pool + paged_offset(pv, seq, c0 + jj, kvh);
-      if ((int)threadIdx.x < hd) acc0 = fmaf(pj, to_f32<T>(vr[threadIdx.x]), acc0);
-      if ((int)threadIdx.x + CHUNK < hd) acc1 = fmaf(pj, to_f32<T>(vr[threadIdx.x + CHUNK]), acc1);
+      const T* vr = v_pool + paged_offset(pv, seq, key, kvh) / hd * v_ld;
+#pragma unroll
+      for (int a = 0; a < MAX_ACC; a++)
+        if ((int)threadIdx.x + a * CHUNK < vd) acc[a] = fmaf(pj, to_f32<T>(vr[threadIdx.x + a * CHUNK]), acc[a]);
     }
     __syncthreads();
   }
-  T* orow = out + ((long long)t * n_heads + h) * hd;
+  T* orow = out + ((long long)t * n_heads + h) * vd;
+  const T* grow = gate ? gate + (long long)t * gate_ld + (long long)h * vd : nullptr;
   const float inv = 1.0f / l;
-  if ((int)threadIdx.x < hd) orow[threadIdx.x] = from_f32<T>(acc0 * inv);
-  if ((int)threadIdx.x + CHUNK < hd) orow[threadIdx.x + CHUNK] = from_f32<T>(acc1 * inv);
+#pragma unroll
+  for (int a = 0; a < MAX_ACC; a++) {
+    const int d = threadIdx.x + a * CHUNK;
+    if (d < vd) {
+      float o = acc[a] * inv;
+      if (grow) o *= 1.0f / (1.0f + expf(-to_f32<T>(grow[d])));
+      orow[d] = from_f32<T>(o);
+    }
+  }
 }
 
-MF_API int mf_attention_generic(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
-                                int T, int n_heads, int n_kv, int hd, const int* positions,
-                                const int* seq_of_token, const int* block_table, int bt_stride,
-                                int page_size, float scale, int window, cudaStream_t stream) {
+static int launch_generic(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype, int T,
+                          int n_heads, int n_kv, int hd, const int* positions, const int* seq_of_token,
+                          const int* block_table, int bt_stride, int page_size, float scale, int window, int vd,
+                          int v_ld, int keep_first, const float* sink, const void* gate, int gate_ld,
+                          cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hd <= 0 || hd > 2 * CHUNK || n_kv <= 0 || n_heads % n_kv) return MF_ERR_BAD_ARG;
-  if (n_heads > 65535) return MF_ERR_BAD_ARG;
+  if (hd <= 0 || hd > 1024 || vd <= 0 || vd > MAX_ACC * CHUNK || v_ld < vd || n_kv <= 0 || n_heads % n_kv)
+    return MF_ERR_BAD_ARG;
+  if (n_heads > 65535 || keep_first < 0) return MF_ERR_BAD_ARG;
   PagedView pv{block_table, bt_stride, page_size, n_kv, hd};
   dim3 grid(T, n_heads);
   const size_t smem = (size_t)(hd + CHUNK) * sizeof(float);
@@ -84,12 +121,32 @@ MF_API int mf_attention_generic(const void* q, const void* k_pool, const void* v
   if (dtype == MF_F32)
     attention_generic_kernel<float><<<grid, CHUNK, smem, stream>>>(
         (const float*)q, (const float*)k_pool, (const float*)v_pool, (float*)out, positions, seq_of_token, pv,
-        n_heads, scale, window);
+        n_heads, scale, window, vd, v_ld, keep_first, sink, (const float*)gate, gate_ld);
   else if (dtype == MF_BF16)
     attention_generic_kernel<__nv_bfloat16><<<grid, CHUNK, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-        (__nv_bfloat16*)out, positions, seq_of_token, pv, n_heads, scale, window);
+        (__nv_bfloat16*)out, positions, seq_of_token, pv, n_heads, scale, window, vd, v_ld, keep_first, sink,
+        (const __nv_bfloat16*)gate, gate_ld);
   else
     return MF_ERR_BAD_DTYPE;
   return (int)cudaGetLastError();
+}
+
+MF_API int mf_attention_generic(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
+                                int T, int n_heads, int n_kv, int hd, const int* positions,
+                                const int* seq_of_token, const int* block_table, int bt_stride,
+                                int page_size, float scale, int window, cudaStream_t stream) {
+  if (hd > 2 * CHUNK) return MF_ERR_BAD_ARG;
+  return launch_generic(q, k_pool, v_pool, out, dtype, T, n_heads, n_kv, hd, positions, seq_of_token, block_table,
+                        bt_stride, page_size, scale, window, hd, hd, 0, nullptr, nullptr, 0, stream);
+}
+
+// The same with the options above: value width and row stride, kept first keys, sink, output gate.
+MF_API int mf_attention_generic_ex(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
+                                   int T, int n_heads, int n_kv, int hd, const int* positions,
+                                   const int* seq_of_token, const int* block_table, int bt_stride,
+                                   int page_size, float scale, int window, int vd, int v_ld, int keep_first,
+                                   const float* sink, const void* gate, int gate_ld, cudaStream_t stream) {
+  return launch_generic(q, k_pool, v_pool, out, dtype, T, n_heads, n_kv, hd, positions, seq_of_token, block_table,
+                        bt_stride, page_size, scale, window, vd, v_ld, keep_first, sink, gate, gate_ld, stream);
 }

@@ -82,6 +82,21 @@ _SIGNATURES = {
     "mf_moe_grouped_max_tiles": [c_int, c_int, c_int],
     "mf_moe_grouped_up": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P],
     "mf_moe_grouped_down": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "mf_gated_act": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "mf_add_rmsnorm_pair": [_P, _P, _P, c_int, _P, _P, c_float, _P, _P, c_int, _P, c_int, c_int, _P],
+    "mf_attention_generic_ex": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,
+                                c_float, c_int, c_int, c_int, c_int, _P, _P, c_int, _P],
+    "mf_rope_store": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int, _P, _P, _P, _P,
+                      _P, c_int, c_int, _P],
+    "mf_latent_prepare": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, c_float, _P, _P, _P, c_int,
+                          c_int, _P, _P, _P, _P, c_int, _P],
+    "mf_latent_query": [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P],
+    "mf_head_linear": [_P, c_longlong, c_int, _P, _P, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, _P,
+                       c_longlong, _P],
+    "mf_retention_prepare": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P, _P, _P],
+    "mf_retention_recurrence": [_P, _P, c_int, c_longlong, _P, _P, c_longlong, _P, _P, _P, _P, c_int, c_int, c_int,
+                                c_int, _P],
+    "mf_retention_output": [_P, _P, c_int, c_longlong, c_float, _P, c_int, c_int, c_int, _P],
 }
 
 MF_ERRORS = {10001: "a size or option this kernel does not take", 10002: "an unsupported dtype"}

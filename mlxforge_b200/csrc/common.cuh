@@ -27,6 +27,14 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// Activations of a gated feed-forward, in 32-bit.
+#define MF_ACT_SILU 0
+#define MF_ACT_GELU_TANH 1      // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float gate_act(float g, int act) {
+  if (act == MF_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -154,6 +162,16 @@ enum MfKernel {
   MF_K_MOE_COMBINE,
   MF_K_MOE_SORT,              // (token, choice) pairs ordered by expert
   MF_K_MOE_GROUPED,           // experts for many tokens: tensor-core tiles over the sorted pairs
+  MF_K_ROPE_STORE,            // rotation in either pairing with the cache write (values may be the unrotated keys)
+  MF_K_NORM_PAIR,             // residual add and two RMS norms of the same sum
+  MF_K_LATENT_PREPARE,        // norms of the two latents, the shared rotated key part, the cache write
+  MF_K_LATENT_QUERY,          // rotated query parts into the queries over the latent
+  MF_K_HEAD_LINEAR,           // a product per head (few tokens)
+  MF_K_HEAD_LINEAR_MMA,       // the same on tensor cores (many tokens)
+  MF_K_RETENTION_PREPARE,     // rotation and key scaling of the retention's operands
+  MF_K_RETENTION_RECURRENCE,  // the decayed state, token after token
+  MF_K_RETENTION_CHUNKED,     // the same over runs of tokens as products
+  MF_K_RETENTION_OUTPUT,      // per-head norm of the read-out and the gate
   MF_K_COUNT
 };
 extern unsigned long long g_mf_kernel_launches[MF_K_COUNT];

@@ -327,12 +327,13 @@ MF_API int mf_rope_kv_write(const void* qkv, int dtype, int T, int n_heads, int 
   return (int)cudaGetLastError();
 }
 
-// ------------------------------------------------------------------ SwiGLU
+// ------------------------------------------------------------------ gated activation
 // gu [T, 2I] holds gate and up interleaved in groups of `group` columns:
 // gate i is column (i / group) * 2 * group + i % group, up i is `group` further.
-// group == I is the plain [gate | up] concatenation.  out[t, i] = silu(gate) * up.
+// group == I is the plain [gate | up] concatenation.  out[t, i] = act(gate) * up with
+// act = SiLU (MF_ACT_SILU) or the tanh form of GELU (MF_ACT_GELU_TANH), in 32-bit.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long n, int I, int group) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long n, int I, int group, int act) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n) return;
   const long long t = idx / I;
@@ -340,11 +341,12 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, lon
   const int col = (i / group) * 2 * group + (i % group);
   const T* row = gu + t * 2 * (long long)I;
   const float g = to_f32<T>(row[col]), u = to_f32<T>(row[col + group]);
-  out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+  out[idx] = from_f32<T>(gate_act(g, act) * u);
 }
 
 // bfloat16 with groups of 8: 16 bytes of gate, 16 bytes of up, 16 bytes out per thread
-__global__ void swiglu_bf16_g8_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out, long long n_groups) {
+__global__ void swiglu_bf16_g8_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out, long long n_groups,
+                                      int act) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_groups) return;
   const uint4 gv = gu[2 * idx], uv = gu[2 * idx + 1];
@@ -355,31 +357,98 @@ __global__ void swiglu_bf16_g8_kernel(const uint4* __restrict__ gu, uint4* __res
 #pragma unroll
   for (int e = 0; e < 4; e++) {
     const float2 g = __bfloat1622float2(gp[e]), u = __bfloat1622float2(up[e]);
-    p[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    p[e] = __floats2bfloat162_rn(gate_act(g.x, act) * u.x, gate_act(g.y, act) * u.y);
   }
   out[idx] = pk;
 }
 
-MF_API int mf_swiglu(const void* gu, void* out, int dtype, int T, int I, int group, cudaStream_t stream) {
+MF_API int mf_gated_act(const void* gu, void* out, int dtype, int T, int I, int group, int act,
+                        cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (group <= 0 || I % group) return MF_ERR_BAD_ARG;
+  if (group <= 0 || I % group || (act != MF_ACT_SILU && act != MF_ACT_GELU_TANH)) return MF_ERR_BAD_ARG;
   if (dtype == MF_BF16 && group == 8 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
     const long long n_groups = (long long)T * (I / 8);
     swiglu_bf16_g8_kernel<<<(unsigned)((n_groups + 255) / 256), 256, 0, stream>>>((const uint4*)gu, (uint4*)out,
-                                                                                    n_groups);
+                                                                                    n_groups, act);
     return (int)cudaGetLastError();
   }
   const long long n = (long long)T * I;
   const int threads = 256;
   const unsigned blocks = (unsigned)((n + threads - 1) / threads);
   if (dtype == MF_F32)
-    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n, I, group);
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n, I, group, act);
   else if (dtype == MF_BF16)
     swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
-                                                                 n, I, group);
+                                                                 n, I, group, act);
   else
     return MF_ERR_BAD_DTYPE;
   return (int)cudaGetLastError();
+}
+
+MF_API int mf_swiglu(const void* gu, void* out, int dtype, int T, int I, int group, cudaStream_t stream) {
+  return mf_gated_act(gu, out, dtype, T, I, group, MF_ACT_SILU, stream);
+}
+
+// ------------------------------------------------------------------ add + two RMSNorms of one sum
+// A layer whose two branches read the same residual: resid += d1 + d2 (either may be null), then
+// out1 = rmsnorm(resid) * w1 and, if asked for, out2 = rmsnorm(resid) * w2: one pass over the row,
+// one sum of squares.  With `rows` only those rows are produced and resid is left as it is.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_pair_kernel(float* __restrict__ resid, const TD* __restrict__ d1,
+                                        const TD* __restrict__ d2, const float* __restrict__ w1,
+                                        const float* __restrict__ w2, float eps, TO* __restrict__ out1,
+                                        TO* __restrict__ out2, const int* __restrict__ rows, int H) {
+  __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const long long src = rows ? rows[r] : r;
+  float* x = resid + src * H;
+  const TD* a = d1 ? d1 + src * H : nullptr;
+  const TD* b = d2 ? d2 + src * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = x[i];
+    if (a || b) {
+      float d = a ? to_f32<TD>(a[i]) : 0.f;
+      if (b) d += to_f32<TD>(b[i]);
+      v += d;
+      if (!rows) x[i] = v;
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  TO* o1 = out1 + (long long)r * H;
+  TO* o2 = out2 ? out2 + (long long)r * H : nullptr;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = x[i];
+    if (rows && (a || b)) {
+      float d = a ? to_f32<TD>(a[i]) : 0.f;
+      if (b) d += to_f32<TD>(b[i]);
+      v += d;
+    }
+    o1[i] = from_f32<TO>(v * inv * w1[i]);
+    if (o2) o2[i] = from_f32<TO>(v * inv * w2[i]);
+  }
+}
+
+MF_API int mf_add_rmsnorm_pair(float* resid, const void* d1, const void* d2, int delta_dtype, const float* w1,
+                               const float* w2, float eps, void* out1, void* out2, int out_dtype, const int* rows,
+                               int n_rows, int H, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (out2 && !w2) return MF_ERR_BAD_ARG;
+  const int threads = H >= 1024 ? 256 : 128;
+  mf_count(MF_K_NORM_PAIR);
+#define LAUNCH(TD, TO)                                                                                        \
+  return (int)launch_dep(add_rmsnorm_pair_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, resid,      \
+                         (const TD*)d1, (const TD*)d2, w1, w2, eps, (TO*)out1, (TO*)out2, rows, H)
+  if (delta_dtype == MF_F32 && out_dtype == MF_F32) LAUNCH(float, float);
+  if (delta_dtype == MF_BF16 && out_dtype == MF_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  if (delta_dtype == MF_F32 && out_dtype == MF_BF16) LAUNCH(float, __nv_bfloat16);
+  if (delta_dtype == MF_BF16 && out_dtype == MF_F32) LAUNCH(__nv_bfloat16, float);
+#undef LAUNCH
+  return MF_ERR_BAD_DTYPE;
 }
 
 // ------------------------------------------------------------------ plain residual add

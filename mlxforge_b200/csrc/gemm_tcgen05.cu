@@ -89,7 +89,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
 }
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+template <int ACT> __device__ __forceinline__ float act_mul(float g, float u) { return gate_act(g, ACT) * u; }
 
 // Stores 32 consecutive columns of one row of the accumulator.
 template <int EPI>
@@ -120,7 +120,7 @@ __device__ __forceinline__ void store_chunk(void* __restrict__ C, const unsigned
       for (int j = 0; j < 32 && col + j < N; j++) dst[j] = __uint_as_float(r[j]);
     }
   } else {
-    // 32 columns = two groups of [8 gate | 8 up] -> 16 outputs at column col / 2
+    // 32 columns = two groups of [8 gate | 8 up] -> 16 outputs at column col / 2 (EPI 2: SiLU, EPI 3: tanh-GELU)
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + (long long)row * (N / 2) + col / 2;
 #pragma unroll
     for (int grp = 0; grp < 2; grp++) {
@@ -128,7 +128,7 @@ __device__ __forceinline__ void store_chunk(void* __restrict__ C, const unsigned
       float o[8];
 #pragma unroll
       for (int j = 0; j < 8; j++)
-        o[j] = silu_mul(__uint_as_float(r[grp * 16 + j]), __uint_as_float(r[grp * 16 + 8 + j]));
+        o[j] = act_mul<EPI == 3 ? MF_ACT_GELU_TANH : MF_ACT_SILU>(__uint_as_float(r[grp * 16 + j]), __uint_as_float(r[grp * 16 + 8 + j]));
       if ((((uintptr_t)(dst + grp * 8)) & 15) == 0) {
         uint4 pk;
         pk.x = pack_bf16(o[0], o[1]); pk.y = pack_bf16(o[2], o[3]);
@@ -276,27 +276,28 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int* stat
   const int n_sms = mf_sm_count();
   if (n_sms <= 0) return MF_ERR_BAD_ARG;
   const int n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  mf_count(EPI == 2 ? MF_K_GEMM_TC_SWIGLU : MF_K_GEMM_TC);
+  mf_count(EPI >= 2 ? MF_K_GEMM_TC_SWIGLU : MF_K_GEMM_TC);
   gemm_kernel<BN, EPI><<<n_tiles < n_sms ? n_tiles : n_sms, 192, smem, stream>>>(ma, mw, C, M, N, K, status);
   return (int)cudaGetLastError();
 }
 
 }  // namespace
 
-// epilogue 0: C bfloat16 [M, N]; 1: C float32 [M, N]; 2: C bfloat16 [M, N/2] = silu(gate) * up for a W
+// epilogue 0: C bfloat16 [M, N]; 1: C float32 [M, N]; 2 (SiLU), 3 (tanh-GELU): C bfloat16 [M, N/2] = act(gate) * up for a W
 // whose rows interleave gate and up in groups of 8 (N a multiple of 16).
 // K must be a multiple of 8 and A, W 16-byte aligned (TMA strides).  `status` as in mf_stream_linear
 // (codes 11: producer, 12: MMA issuer, 13: epilogue).
 MF_API int mf_gemm_bf16(const void* A, const void* W, void* C, int M, int N, int K, int epilogue, int* status,
                         cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 || epilogue < 0 || epilogue > 2) return MF_ERR_BAD_ARG;
-  if (epilogue == 2 && N % 16) return MF_ERR_BAD_ARG;
+  if (K <= 0 || K % 8 || epilogue < 0 || epilogue > 3) return MF_ERR_BAD_ARG;
+  if (epilogue >= 2 && N % 16) return MF_ERR_BAD_ARG;
   if (((uintptr_t)A | (uintptr_t)W) & 15) return MF_ERR_BAD_ARG;
   const bool wide = N > 128;
   switch (epilogue) {
     case 0: return wide ? launch<256, 0>(A, W, C, M, N, K, status, stream) : launch<128, 0>(A, W, C, M, N, K, status, stream);
     case 1: return wide ? launch<256, 1>(A, W, C, M, N, K, status, stream) : launch<128, 1>(A, W, C, M, N, K, status, stream);
-    default: return wide ? launch<256, 2>(A, W, C, M, N, K, status, stream) : launch<128, 2>(A, W, C, M, N, K, status, stream);
+    case 2: return wide ? launch<256, 2>(A, W, C, M, N, K, status, stream) : launch<128, 2>(A, W, C, M, N, K, status, stream);
+    default: return wide ? launch<256, 3>(A, W, C, M, N, K, status, stream) : launch<128, 3>(A, W, C, M, N, K, status, stream);
   }
 }

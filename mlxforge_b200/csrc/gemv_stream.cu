@@ -212,7 +212,7 @@ stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restri
           gs += red[(w * ROWS + r) * RED_M + m];
           us += red[(w * ROWS + r + HALF) * RED_M + m];
         }
-        out[(long long)m * (N / 2) + tile * HALF + r] = from_f32<OutT>(gs / (1.0f + expf(-gs)) * us);
+        out[(long long)m * (N / 2) + tile * HALF + r] = from_f32<OutT>(gate_act(gs, mode == 2 ? MF_ACT_GELU_TANH : MF_ACT_SILU) * us);
       }
     }
     consumer_sync();       // `red` is free for the next tile
@@ -360,7 +360,7 @@ stream_tmap_kernel(const __nv_bfloat16* __restrict__ x, const __grid_constant__ 
           gs += red[(w * ROWS + r) * RED_M + m];
           us += red[(w * ROWS + r + HALF) * RED_M + m];
         }
-        out[(long long)m * (N / 2) + tile * HALF + r] = from_f32<OutT>(gs / (1.0f + expf(-gs)) * us);
+        out[(long long)m * (N / 2) + tile * HALF + r] = from_f32<OutT>(gate_act(gs, mode == 2 ? MF_ACT_GELU_TANH : MF_ACT_SILU) * us);
       }
     }
     consumer_sync();       // `red` is free for the next tile
@@ -460,15 +460,15 @@ MF_API int mf_set_stream_tensor_copies(int on) {
   return 0;
 }
 
-// mode 0: out [M, N] in out_dtype.  mode 1: W rows interleave gate and up in groups of 8 (N a
-// multiple of 16) and out is [M, N / 2] = silu(gate) * up.  K must be a multiple of 8 and x, W
+// mode 0: out [M, N] in out_dtype.  mode 1 (SiLU) and 2 (tanh form of GELU): W rows interleave gate and up in groups of 8 (N a
+// multiple of 16) and out is [M, N / 2] = act(gate) * up.  K must be a multiple of 8 and x, W
 // 16-byte aligned.  `status`: a device int (may be null) that receives a non-zero code if a wait
 // inside the kernel ran out (1: producer, 2: consumer).
 MF_API int mf_stream_linear(const void* x, const void* W, void* out, int out_dtype, int M, int N, int K, int mode,
                             int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || K % 8 || M > 16 || (mode != 0 && mode != 1)) return MF_ERR_BAD_ARG;
-  if (mode == 1 && N % 16) return MF_ERR_BAD_ARG;
+  if (K <= 0 || K % 8 || M > 16 || mode < 0 || mode > 2) return MF_ERR_BAD_ARG;
+  if (mode != 0 && N % 16) return MF_ERR_BAD_ARG;
   if (((uintptr_t)x | (uintptr_t)W) & 15) return MF_ERR_BAD_ARG;
   const __nv_bfloat16 *xx = (const __nv_bfloat16*)x, *ww = (const __nv_bfloat16*)W;
   if (out_dtype == MF_BF16) return dispatch<__nv_bfloat16>(xx, ww, (__nv_bfloat16*)out, M, N, K, mode, status, stream);

@@ -12,6 +12,8 @@ const char* const kNames[MF_K_COUNT] = {
     "embed_positions",  "hyper_norm",       "kv_store",         "attn_talking",     "attn_talking_tc", "attn_talking_merge",
     "delta_prepare",    "delta_gates",      "delta_recurrence", "delta_output",
     "moe_route",        "moe_rows",         "moe_combine",      "moe_sort",         "moe_grouped",
+    "rope_store",       "norm_pair",        "latent_prepare",   "latent_query",     "head_linear",
+    "head_linear_mma",  "retention_prepare", "retention_recurrence", "retention_chunked", "retention_output",
 };
 int g_sm_count[MF_MAX_DEVICES] = {};
 }  // namespace

@@ -1,0 +1,165 @@
+// Kernels around attention over a compressed latent: every token keeps one normed latent vector
+// c [rank] and one rotated key part r [rot] that all heads share, `rank + rot` numbers in a cache
+// lane of one key head.  With per-head expansions K_h = U_k,h c and V_h = U_v,h c the score of
+// query (n_h | p_h) against a token is  n_h . (U_k,h c) + p_h . r  =  (U_k,h^T n_h) . c + p_h . r,
+// so the attention runs over the latent itself: queries are (U_k,h^T n_h | p_h), `rank + rot`
+// wide, keys are the cached rows, values their first `rank` channels, and the head's output is
+// U_v,h applied to the attended latent.  Nothing is ever expanded per cached token.
+//
+//  * latent_prepare: one block per token over a row of projections [dq | dkv | ...]: the RMS norm
+//    of the query latent, the RMS norm of the key/value latent and the half-split rotation of
+//    the shared key part, the last two written into the token's place in the cache.
+//  * latent_query: the rotated parts of the queries moved (rotated) behind the absorbed parts.
+//  * head_linear: a product per head, out[t, h, :] = W_h x[t, h, :] with W [heads, N, K], rows
+//    and heads of x and out at given strides, optionally times sigmoid(gate); accumulation in
+//    32-bit, a warp per output element.  For few tokens; many tokens take the tensor-core one.
+#include "rotary.cuh"
+
+template <typename T>
+__global__ void latent_prepare_kernel(const T* __restrict__ proj, int ld, int q_rank, int kv_off, int rank, int rot,
+                                      const float* __restrict__ wq, const float* __restrict__ wkv, float eps,
+                                      const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                      PagedView pv, const float* __restrict__ inv_f, const double* __restrict__ inv_d,
+                                      T* __restrict__ cq_out, T* __restrict__ k_pool, int write_kv) {
+  __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const T* row = proj + (long long)t * ld;
+  {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
+      const float v = to_f32<T>(row[i]);
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)q_rank + eps);
+    T* o = cq_out + (long long)t * q_rank;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) o[i] = from_f32<T>(to_f32<T>(row[i]) * inv * wq[i]);
+  }
+  if (!write_kv) return;
+  const int pos = positions[t], seq = seq_of_token[t];
+  const T* kv = row + kv_off;
+  T* dst = k_pool + paged_offset(pv, seq, pos, 0);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+    const float v = to_f32<T>(kv[i]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32<T>(kv[i]) * inv * wkv[i]);
+  const int half = rot >> 1;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) {
+    float c, s;
+    rotary_cs(pos, j, inv_f, inv_d, c, s);
+    const float u = to_f32<T>(kv[rank + j]), v = to_f32<T>(kv[rank + j + half]);
+    dst[rank + j] = from_f32<T>(u * c - v * s);
+    dst[rank + j + half] = from_f32<T>(v * c + u * s);
+  }
+}
+
+MF_API int mf_latent_prepare(const void* proj, int dtype, int T, int ld, int q_rank, int kv_off, int rank, int rot,
+                             const float* wq, const float* wkv, float eps, const int* positions,
+                             const int* seq_of_token, const int* block_table, int bt_stride, int page_size,
+                             const float* inv_f, const double* inv_d, void* cq_out, void* k_pool, int write_kv,
+                             cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (q_rank <= 0 || rank <= 0 || rot < 0 || (rot & 1)) return MF_ERR_BAD_ARG;
+  PagedView pv{block_table, bt_stride, page_size, 1, rank + rot};
+  mf_count(MF_K_LATENT_PREPARE);
+  if (dtype == MF_F32)
+    return (int)launch_dep(latent_prepare_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)proj, ld, q_rank,
+                           kv_off, rank, rot, wq, wkv, eps, positions, seq_of_token, pv, inv_f, inv_d, (float*)cq_out,
+                           (float*)k_pool, write_kv);
+  if (dtype == MF_BF16)
+    return (int)launch_dep(latent_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream,
+                           (const __nv_bfloat16*)proj, ld, q_rank, kv_off, rank, rot, wq, wkv, eps, positions,
+                           seq_of_token, pv, inv_f, inv_d, (__nv_bfloat16*)cq_out, (__nv_bfloat16*)k_pool, write_kv);
+  return MF_ERR_BAD_DTYPE;
+}
+
+// q [T, heads, dim + rot] -> q_full[t, h, rank : rank + rot] = rotation of q[t, h, dim : dim + rot]
+template <typename T>
+__global__ void latent_query_kernel(const T* __restrict__ q, int n_heads, int dim, int rot, int rank,
+                                    const int* __restrict__ positions, const float* __restrict__ inv_f,
+                                    const double* __restrict__ inv_d, T* __restrict__ q_full) {
+  pdl_launch();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rot >> 1;
+  pdl_wait();
+  for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
+    const int h = idx / half, j = idx - h * half;
+    float c, s;
+    rotary_cs(pos, j, inv_f, inv_d, c, s);
+    const T* src = q + ((long long)t * n_heads + h) * (dim + rot) + dim;
+    T* dst = q_full + ((long long)t * n_heads + h) * (rank + rot) + rank;
+    const float u = to_f32<T>(src[j]), v = to_f32<T>(src[j + half]);
+    dst[j] = from_f32<T>(u * c - v * s);
+    dst[j + half] = from_f32<T>(v * c + u * s);
+  }
+}
+
+MF_API int mf_latent_query(const void* q, int dtype, int T, int n_heads, int dim, int rot, int rank,
+                           const int* positions, const float* inv_f, const double* inv_d, void* q_full,
+                           cudaStream_t stream) {
+  if (T <= 0 || rot == 0) return 0;
+  if (rot < 0 || (rot & 1)) return MF_ERR_BAD_ARG;
+  mf_count(MF_K_LATENT_QUERY);
+  if (dtype == MF_F32)
+    return (int)launch_dep(latent_query_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)q, n_heads, dim,
+                           rot, rank, positions, inv_f, inv_d, (float*)q_full);
+  if (dtype == MF_BF16)
+    return (int)launch_dep(latent_query_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)q,
+                           n_heads, dim, rot, rank, positions, inv_f, inv_d, (__nv_bfloat16*)q_full);
+  return MF_ERR_BAD_DTYPE;
+}
+
+// ---------------------------------------------------------------------------- a product per head
+constexpr int HL_WARPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(HL_WARPS * 32)
+head_linear_kernel(const T* __restrict__ x, long long x_ld, int x_hs, const T* __restrict__ w, T* __restrict__ out,
+                   long long out_ld, int out_hs, int N, int K, const T* __restrict__ gate, long long gate_ld) {
+  extern __shared__ float xs[];          // [K]
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const T* xr = x + t * x_ld + (long long)h * x_hs;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f32<T>(xr[k]);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* wh = w + (long long)h * N * K;
+  T* orow = out + t * out_ld + (long long)h * out_hs;
+  const T* grow = gate ? gate + t * gate_ld + (long long)h * N : nullptr;
+  for (int n = warp; n < N; n += HL_WARPS) {
+    const T* wr = wh + (long long)n * K;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], to_f32<T>(wr[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      if (grow) acc *= 1.0f / (1.0f + expf(-to_f32<T>(grow[n])));
+      orow[n] = from_f32<T>(acc);
+    }
+  }
+}
+
+MF_API int mf_head_linear(const void* x, long long x_ld, int x_hs, const void* w, void* out, long long out_ld,
+                          int out_hs, int dtype, int T, int n_heads, int N, int K, const void* gate,
+                          long long gate_ld, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (n_heads <= 0 || n_heads > 65535 || N <= 0 || K <= 0 || K > 8192) return MF_ERR_BAD_ARG;
+  const size_t smem = (size_t)K * sizeof(float);
+  mf_count(MF_K_HEAD_LINEAR);
+  if (dtype == MF_F32)
+    return (int)launch_dep(head_linear_kernel<float>, dim3(T, n_heads), dim3(HL_WARPS * 32), smem, stream,
+                           (const float*)x, x_ld, x_hs, (const float*)w, (float*)out, out_ld, out_hs, N, K,
+                           (const float*)gate, gate_ld);
+  if (dtype == MF_BF16)
+    return (int)launch_dep(head_linear_kernel<__nv_bfloat16>, dim3(T, n_heads), dim3(HL_WARPS * 32), smem, stream,
+                           (const __nv_bfloat16*)x, x_ld, x_hs, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_ld,
+                           out_hs, N, K, (const __nv_bfloat16*)gate, gate_ld);
+  return MF_ERR_BAD_DTYPE;
+}

@@ -81,10 +81,132 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torc
                                      _stream()), "rope_kv_write")
 
 
-def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int) -> None:
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def activation_code(act: str) -> int:
+    try:
+        return ACTIVATIONS[act]
+    except KeyError:
+        raise KernelError(f"unknown gate activation '{act}' (one of {sorted(ACTIVATIONS)})") from None
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int, act: str = "silu") -> None:
+    """out = act(gate) * up for gate and up interleaved in groups of ``group`` columns."""
     _need_cuda(gu, out)
     T, I = out.shape
-    check(library().mf_swiglu(gu.data_ptr(), out.data_ptr(), dtype_code(gu), T, I, group, _stream()), "swiglu")
+    check(library().mf_gated_act(gu.data_ptr(), out.data_ptr(), dtype_code(gu), T, I, group, activation_code(act),
+                                 _stream()), "gated_act")
+
+
+def add_rmsnorm_pair(resid: torch.Tensor, d1: Optional[torch.Tensor], d2: Optional[torch.Tensor], w1: torch.Tensor,
+                     w2: Optional[torch.Tensor], eps: float, out1: torch.Tensor, out2: Optional[torch.Tensor],
+                     rows: Optional[torch.Tensor] = None) -> None:
+    """``resid += d1 + d2`` (either may be None), then ``out1 = rmsnorm(resid) * w1`` and, where asked for,
+    ``out2 = rmsnorm(resid) * w2``.  With ``rows`` only those rows are produced and ``resid`` stays."""
+    _need_cuda(resid, d1, d2, w1, w2, out1, out2, rows)
+    if d1 is not None and d2 is not None and d1.dtype != d2.dtype:
+        raise KernelError("add_rmsnorm_pair: the two deltas must have one dtype")
+    d = d1 if d1 is not None else d2
+    check(library().mf_add_rmsnorm_pair(resid.data_ptr(), _ptr(d1), _ptr(d2), dtype_code(d) if d is not None else F32,
+                                        w1.data_ptr(), _ptr(w2), eps, out1.data_ptr(), _ptr(out2), dtype_code(out1),
+                                        _ptr(rows), out1.shape[0], resid.shape[-1], _stream()), "add_rmsnorm_pair")
+
+
+def rope_store(qk: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+               page_size: int, inv_f: Optional[torch.Tensor], inv_d: Optional[torch.Tensor], q_out: torch.Tensor,
+               k_pool: torch.Tensor, v_pool: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, rotary_dim: int,
+               pairs: bool, write_kv: bool, v_from_k: bool, ld: Optional[int] = None) -> None:
+    """Rotation of queries and keys (``pairs``: channel 2i with 2i+1, else i with i + rotary_dim/2) with the
+    cache write; ``v_from_k``: the rows hold no values and the value pages get the keys before rotation.
+    ``inv_d`` (float64 inverse wavelengths) selects angles in double, else ``inv_f`` (float32).  Rows of
+    ``qk`` are ``ld`` elements apart (default: as wide as their heads)."""
+    _need_cuda(positions, seq_of_token, block_table, inv_f, inv_d, q_out, k_pool, v_pool)
+    if ld is None:
+        ld = (n_heads + (1 if v_from_k else 2) * n_kv) * head_dim
+    check(library().mf_rope_store(qk.data_ptr(), ld, dtype_code(qk), qk.shape[0], n_heads, n_kv, head_dim, rotary_dim,
+                                  1 if pairs else 0, positions.data_ptr(), seq_of_token.data_ptr(),
+                                  block_table.data_ptr(), block_table.shape[1], page_size, _ptr(inv_f), _ptr(inv_d),
+                                  q_out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), int(write_kv), int(v_from_k),
+                                  _stream()), "rope_store")
+
+
+def attention_generic_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                         positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                         page_size: int, n_heads: int, n_kv: int, head_dim: int, scale: float, window: int,
+                         v_dim: int, v_ld: int, keep_first: int = 0, sink: Optional[torch.Tensor] = None,
+                         gate: Optional[torch.Tensor] = None, gate_ld: int = 0) -> None:
+    """The block-per-token attention with its options: values ``v_dim`` wide in rows ``v_ld`` apart
+    (``v_pool`` may be ``k_pool``), the first ``keep_first`` keys kept beside the window, a sink per head in
+    the softmax denominator, the output times sigmoid(``gate``) (rows ``gate_ld`` apart)."""
+    _need_cuda(q, k_pool, v_pool, out, positions, seq_of_token, block_table, sink)
+    check(library().mf_attention_generic_ex(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+                                            dtype_code(q), q.shape[0], n_heads, n_kv, head_dim, positions.data_ptr(),
+                                            seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                                            page_size, scale, window, v_dim, v_ld, keep_first, _ptr(sink),
+                                            _ptr(gate), gate_ld, _stream()), "attention_generic")
+
+
+def latent_prepare(proj: torch.Tensor, q_rank: int, kv_off: int, rank: int, rot: int, wq: torch.Tensor,
+                   wkv: Optional[torch.Tensor], eps: float, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                   block_table: torch.Tensor, page_size: int, inv_f, inv_d, cq_out: torch.Tensor,
+                   k_pool: torch.Tensor, write_kv: bool) -> None:
+    """From rows of projections [query latent | key/value latent, shared key part | ...]: the normed query
+    latent into ``cq_out`` and, if ``write_kv``, the normed latent and the rotated key part into the cache."""
+    _need_cuda(proj, wq, wkv, cq_out, k_pool)
+    check(library().mf_latent_prepare(proj.data_ptr(), dtype_code(proj), proj.shape[0], proj.shape[1], q_rank, kv_off,
+                                      rank, rot, wq.data_ptr(), _ptr(wkv), eps, positions.data_ptr(),
+                                      seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
+                                      _ptr(inv_f), _ptr(inv_d), cq_out.data_ptr(), k_pool.data_ptr(), int(write_kv),
+                                      _stream()), "latent_prepare")
+
+
+def latent_query(q: torch.Tensor, n_heads: int, dim: int, rot: int, rank: int, positions: torch.Tensor, inv_f, inv_d,
+                 q_full: torch.Tensor) -> None:
+    """The rotated part of every head's query, rotated, into columns [rank, rank + rot) of ``q_full``."""
+    _need_cuda(q, q_full)
+    check(library().mf_latent_query(q.data_ptr(), dtype_code(q), q.shape[0], n_heads, dim, rot, rank,
+                                    positions.data_ptr(), _ptr(inv_f), _ptr(inv_d), q_full.data_ptr(), _stream()),
+          "latent_query", launches=1 if rot else 0)
+
+
+def head_linear(x: torch.Tensor, x_ld: int, x_hs: int, w: torch.Tensor, out: torch.Tensor, out_ld: int, out_hs: int,
+                T: int, gate: Optional[torch.Tensor] = None, gate_ld: int = 0) -> None:
+    """``out[t, h, :N] = w[h] @ x[t, h, :K]`` for ``w`` [heads, N, K]; rows of ``x`` / ``out`` are ``x_ld`` /
+    ``out_ld`` elements apart and heads ``x_hs`` / ``out_hs``; optionally times sigmoid(``gate[t, h * N + n]``)."""
+    _need_cuda(w)
+    if x.dtype != w.dtype or out.dtype != w.dtype:
+        raise KernelError("head_linear: operands of one dtype")
+    H, N, K = w.shape
+    check(library().mf_head_linear(x.data_ptr(), x_ld, x_hs, w.data_ptr(), out.data_ptr(), out_ld, out_hs,
+                                   dtype_code(w), T, H, N, K, _ptr(gate), gate_ld, _stream()), "head_linear")
+
+
+def retention_prepare(proj: torch.Tensor, n_heads: int, dim: int, rot: int, k_scale: float, positions: torch.Tensor,
+                      inv_f, inv_d, qk: torch.Tensor) -> None:
+    """Rows [queries | keys | ...] -> 32-bit [T, 2 heads dim]: both rotated, keys times ``k_scale``."""
+    _need_cuda(proj, qk)
+    check(library().mf_retention_prepare(proj.data_ptr(), dtype_code(proj), proj.shape[0], proj.shape[1], n_heads, dim,
+                                         rot, k_scale, positions.data_ptr(), _ptr(inv_f), _ptr(inv_d), qk.data_ptr(),
+                                         _stream()), "retention_prepare")
+
+
+def retention_recurrence(qk: torch.Tensor, v: torch.Tensor, v_ld: int, decay: torch.Tensor, state: torch.Tensor,
+                         batch, o_out: torch.Tensor, n_heads: int, dim: int, vdim: int) -> None:
+    """``v`` points at the first value of the first token (rows ``v_ld`` elements apart)."""
+    _need_cuda(qk, decay, state, o_out)
+    check(library().mf_retention_recurrence(qk.data_ptr(), v.data_ptr(), dtype_code(v), v_ld, decay.data_ptr(),
+                                            state.data_ptr(), state.stride(0), batch.seq_q_start.data_ptr(),
+                                            batch.seq_q_len.data_ptr(), batch.slots.data_ptr(), o_out.data_ptr(),
+                                            batch.n_seqs, n_heads, dim, vdim, _stream()), "retention_recurrence")
+
+
+def retention_output(o: torch.Tensor, gate: torch.Tensor, gate_ld: int, eps: float, out: torch.Tensor, n_heads: int,
+                     vdim: int) -> None:
+    """``gate`` points at the first gate of the first token; rows are ``gate_ld`` elements apart."""
+    _need_cuda(o, out)
+    check(library().mf_retention_output(o.data_ptr(), gate.data_ptr(), dtype_code(out), gate_ld, eps, out.data_ptr(),
+                                        o.shape[0], n_heads, vdim, _stream()), "retention_output")
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
@@ -182,7 +304,8 @@ def set_stream_tensor_copies(on: bool) -> None:
     check(library().mf_set_stream_tensor_copies(1 if on else 0), "set_stream_tensor_copies", launches=0)
 
 
-def stream_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
+def stream_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
+                  act: str = "silu") -> None:
     """out = x @ w^T for at most ``stream_max_rows()`` rows of bfloat16 x (out bfloat16 or
     float32), the weights streamed by bulk copies (see gemv_stream.cu); with ``swiglu`` the rows
     of w interleave gate and up in groups of 8 and out [M, N/2] is silu(gate) * up.
@@ -196,7 +319,8 @@ def stream_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: b
     if w.shape[1] != K or tuple(out.shape) != want:
         raise KernelError(f"stream_linear: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     check(library().mf_stream_linear(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out), M, N, K,
-                                     1 if swiglu else 0, kernel_status(x.device).data_ptr(), _stream()),
+                                     1 + activation_code(act) if swiglu else 0, kernel_status(x.device).data_ptr(),
+                                     _stream()),
           "stream_linear")
 
 
@@ -235,7 +359,7 @@ def gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False, act: str = "silu") -> None:
     """out = x @ w^T on the tcgen05 tensor cores (bfloat16 operands; out bfloat16 or float32);
     with ``swiglu`` the rows of w interleave gate and up in groups of 8 and out is
     [M, N/2] = silu(gate) * up."""
@@ -247,7 +371,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool 
         raise KernelError(f"gemm_bf16: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     if swiglu and out.dtype != torch.bfloat16:
         raise KernelError("gemm_bf16: the gated epilogue writes bfloat16")
-    epi = 2 if swiglu else (1 if out.dtype == torch.float32 else 0)
+    epi = 2 + activation_code(act) if swiglu else (1 if out.dtype == torch.float32 else 0)
     check(library().mf_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, epi,
                                  kernel_status(x.device).data_ptr(), _stream()), "gemm_bf16")
 

@@ -1,0 +1,200 @@
+// Retention: linear attention with a fixed decay per head and no softmax.  Per head, with a
+// 32-bit state S [dim, vdim] per request that starts at zero:
+//
+//     S_t = decay_h S_(t-1) + k_t v_t^T ,     o_t = S_t^T q_t
+//
+// q and k are rotated by position (half-split pairs over the first `rot` channels), k is then
+// multiplied by `k_scale`; each head's o_t is divided by its root mean square (no weight),
+// multiplied by silu(gate) and handed to the output projection.
+//
+//  * retention_prepare: one block per token; rotation and key scaling into 32-bit [T, 2 heads dim].
+//  * retention_recurrence: every column of S is independent, so the recurrence is parallel over
+//    (sequence, head, column) and serial in time only.  Eight lanes share a column and hold
+//    dim/8 of its rows in registers; q and k of the coming tokens are staged in shared memory,
+//    eight tokens at a time.  A step continues from the slot's state, so the result does not
+//    depend on how a prompt was cut.
+//  * retention_output: per token and head the read-out over its root mean square, times silu(gate).
+#include "rotary.cuh"
+
+namespace {
+constexpr int RT_LANES = 8;                 // lanes that share one column of S
+constexpr int RT_COLS = 16;                 // columns per block
+constexpr int RT_THREADS = RT_LANES * RT_COLS;
+constexpr int RT_CHUNK = 8;                 // tokens staged at a time
+}  // namespace
+
+template <typename T>
+__global__ void retention_prepare_kernel(const T* __restrict__ proj, int ld, int n_heads, int dim, int rot,
+                                         float k_scale, const int* __restrict__ positions,
+                                         const float* __restrict__ inv_f, const double* __restrict__ inv_d,
+                                         float* __restrict__ qk) {
+  extern __shared__ float cs[];            // [half] cos, [half] sin
+  pdl_launch();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rot >> 1;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) rotary_cs(pos, j, inv_f, inv_d, cs[j], cs[half + j]);
+  __syncthreads();
+  pdl_wait();
+  const T* row = proj + (long long)t * ld;
+  float* out = qk + (long long)t * 2 * n_heads * dim;
+  const int per_head = dim - half;
+  for (int idx = threadIdx.x; idx < 2 * n_heads * per_head; idx += blockDim.x) {
+    const int h = idx / per_head, j = idx - h * per_head;       // heads 0..n-1: queries, n..2n-1: keys
+    const T* src = row + (long long)h * dim;
+    float* dst = out + (long long)h * dim;
+    const float f = h >= n_heads ? k_scale : 1.0f;
+    if (j < half) {
+      const float c = cs[j], s = cs[half + j];
+      const float u = to_f32<T>(src[j]), v = to_f32<T>(src[j + half]);
+      dst[j] = (u * c - v * s) * f;
+      dst[j + half] = (v * c + u * s) * f;
+    } else {
+      const int ch = rot + (j - half);
+      dst[ch] = to_f32<T>(src[ch]) * f;
+    }
+  }
+}
+
+MF_API int mf_retention_prepare(const void* proj, int dtype, int T, int ld, int n_heads, int dim, int rot,
+                                float k_scale, const int* positions, const float* inv_f, const double* inv_d,
+                                float* qk, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (rot < 0 || rot > dim || (rot & 1) || (rot > 0 && !inv_f && !inv_d)) return MF_ERR_BAD_ARG;
+  const size_t smem = (size_t)(rot > 0 ? rot : 1) * sizeof(float);
+  mf_count(MF_K_RETENTION_PREPARE);
+  if (dtype == MF_F32)
+    return (int)launch_dep(retention_prepare_kernel<float>, dim3(T), dim3(256), smem, stream, (const float*)proj, ld,
+                           n_heads, dim, rot, k_scale, positions, inv_f, inv_d, qk);
+  if (dtype == MF_BF16)
+    return (int)launch_dep(retention_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream,
+                           (const __nv_bfloat16*)proj, ld, n_heads, dim, rot, k_scale, positions, inv_f, inv_d, qk);
+  return MF_ERR_BAD_DTYPE;
+}
+
+// qk [T, 2 heads dim] (32-bit, prepared); v read from the projections' rows (v + t * v_ld + h * vdim).
+// state [slots, heads, dim, vdim] with `state_stride` floats per slot.  o_out [T, heads * vdim] 32-bit.
+template <typename T, int RPL>
+__global__ void __launch_bounds__(RT_THREADS)
+retention_recurrence_kernel(const float* __restrict__ qk, const T* __restrict__ v, long long v_ld,
+                            const float* __restrict__ decay, float* __restrict__ state, long long state_stride,
+                            const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                            const int* __restrict__ slots, float* __restrict__ o_out, int n_heads, int dim, int vdim) {
+  extern __shared__ float sm[];            // [RT_CHUNK][2 dim] q then k of a token, [RT_CHUNK][RT_COLS] v
+  float* v_s = sm + RT_CHUNK * 2 * dim;
+  pdl_launch();
+  pdl_wait();
+  const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * RT_COLS;
+  const int lane = threadIdx.x % RT_LANES, cl = threadIdx.x / RT_LANES;
+  const int c = c0 + cl;
+  const bool col_ok = c < vdim;
+  const int t0 = seq_q_start[s], n = seq_q_len[s];
+  const float g = decay[h];
+  float* S = state + (long long)slots[s] * state_stride + (long long)h * dim * vdim;
+  float st[RPL];
+#pragma unroll
+  for (int i = 0; i < RPL; i++) {
+    const int r = lane + i * RT_LANES;
+    st[i] = (col_ok && r < dim) ? S[(long long)r * vdim + c] : 0.f;
+  }
+  for (int b = 0; b < n; b += RT_CHUNK) {
+    const int nb = min(RT_CHUNK, n - b);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb * 2 * dim; i += RT_THREADS) {
+      const int tt = i / (2 * dim), d = i - tt * 2 * dim;
+      const int hh = d / dim, ch = d - hh * dim;         // 0: q, 1: k
+      sm[i] = qk[(long long)(t0 + b + tt) * 2 * n_heads * dim + (long long)(hh * n_heads + h) * dim + ch];
+    }
+    for (int i = threadIdx.x; i < nb * RT_COLS; i += RT_THREADS) {
+      const int tt = i / RT_COLS, cc = i - tt * RT_COLS;
+      v_s[i] = (c0 + cc < vdim) ? to_f32<T>(v[(long long)(t0 + b + tt) * v_ld + (long long)h * vdim + c0 + cc]) : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nb; tt++) {
+      const float* qs = sm + tt * 2 * dim;
+      const float* ks = qs + dim;
+      const float vc = v_s[tt * RT_COLS + cl];
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < RPL; i++) {
+        const int r = lane + i * RT_LANES;
+        if (r < dim) {
+          st[i] = fmaf(g, st[i], ks[r] * vc);
+          acc = fmaf(st[i], qs[r], acc);
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (lane == 0 && col_ok) o_out[(long long)(t0 + b + tt) * n_heads * vdim + (long long)h * vdim + c] = acc;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RPL; i++) {
+    const int r = lane + i * RT_LANES;
+    if (col_ok && r < dim) S[(long long)r * vdim + c] = st[i];
+  }
+}
+
+MF_API int mf_retention_recurrence(const float* qk, const void* v, int v_dtype, long long v_ld, const float* decay,
+                                   float* state, long long state_stride, const int* seq_q_start,
+                                   const int* seq_q_len, const int* slots, float* o_out, int n_seqs, int n_heads,
+                                   int dim, int vdim, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (dim <= 0 || dim > 32 * RT_LANES || vdim <= 0 || n_heads <= 0 || n_heads > 65535) return MF_ERR_BAD_ARG;
+  dim3 grid(n_seqs, n_heads, (vdim + RT_COLS - 1) / RT_COLS);
+  const size_t smem = (size_t)RT_CHUNK * (2 * dim + RT_COLS) * sizeof(float);
+  const int per = (dim + RT_LANES - 1) / RT_LANES;
+  mf_count(MF_K_RETENTION_RECURRENCE);
+#define RT_LAUNCH(TT, RPL)                                                                                       \
+  return (int)launch_dep(retention_recurrence_kernel<TT, RPL>, grid, dim3(RT_THREADS), smem, stream, qk,         \
+                         (const TT*)v, v_ld, decay, state, state_stride, seq_q_start, seq_q_len, slots, o_out,   \
+                         n_heads, dim, vdim)
+#define RT_PICK(TT)              \
+  if (per <= 4) RT_LAUNCH(TT, 4);  \
+  if (per <= 8) RT_LAUNCH(TT, 8);  \
+  if (per <= 16) RT_LAUNCH(TT, 16); \
+  RT_LAUNCH(TT, 32)
+  if (v_dtype == MF_F32) { RT_PICK(float); }
+  if (v_dtype == MF_BF16) { RT_PICK(__nv_bfloat16); }
+#undef RT_PICK
+#undef RT_LAUNCH
+  return MF_ERR_BAD_DTYPE;
+}
+
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]); a warp per (token, head)
+template <typename T>
+__global__ void retention_output_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long gate_ld,
+                                        float eps, T* __restrict__ out, int n_heads, int vdim) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int h = warp; h < n_heads; h += nw) {
+    const float* orow = o + ((long long)t * n_heads + h) * vdim;
+    const T* grow = gate + (long long)t * gate_ld + (long long)h * vdim;
+    float ss = 0.f;
+    for (int d = lane; d < vdim; d += 32) ss += orow[d] * orow[d];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    T* dst = out + ((long long)t * n_heads + h) * vdim;
+    for (int d = lane; d < vdim; d += 32) {
+      const float g = to_f32<T>(grow[d]);
+      dst[d] = from_f32<T>(orow[d] * inv * (g / (1.0f + expf(-g))));
+    }
+  }
+}
+
+MF_API int mf_retention_output(const float* o, const void* gate, int dtype, long long gate_ld, float eps, void* out,
+                               int T, int n_heads, int vdim, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  mf_count(MF_K_RETENTION_OUTPUT);
+  const int threads = n_heads >= 8 ? 256 : 32 * (n_heads > 0 ? n_heads : 1);
+  if (dtype == MF_F32)
+    return (int)launch_dep(retention_output_kernel<float>, dim3(T), dim3(threads), 0, stream, o, (const float*)gate,
+                           gate_ld, eps, (float*)out, n_heads, vdim);
+  if (dtype == MF_BF16)
+    return (int)launch_dep(retention_output_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, o,
+                           (const __nv_bfloat16*)gate, gate_ld, eps, (__nv_bfloat16*)out, n_heads, vdim);
+  return MF_ERR_BAD_DTYPE;
+}

@@ -110,6 +110,14 @@ class Runtime:
             torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
         return out
 
+    def head_linear(self, x, x_ld: int, x_hs: int, w, out, out_ld: int, out_hs: int, T: int, gate=None,
+                    gate_ld: int = 0):
+        """A product per head: ``out[t, h, :] = w[h] @ x[t, h, :]`` for ``w`` [heads, N, K], rows and heads of
+        ``x`` and ``out`` at the given strides (in elements), optionally times ``sigmoid(gate[t, h * N + n])``;
+        32-bit accumulation, one rounding."""
+        ops.head_linear(x, x_ld, x_hs, w, out, out_ld, out_hs, T, gate, gate_ld)
+        return out
+
     def _skinny(self, x, w) -> bool:
         return self.skinny_enabled and x.shape[0] <= self.stream_max_rows and ops.few_rows_ok(x, w)
 
@@ -117,22 +125,23 @@ class Runtime:
         return ((self.mid_rows_enabled or self.gemm_backend == "tcgen05") and self.gemm_backend != "library"
                 and x.shape[0] <= self.mid_max_rows and ops.gemm_ok(x, w))
 
-    def linear_swiglu(self, x: torch.Tensor, w_gu: torch.Tensor, group: int, out: torch.Tensor) -> torch.Tensor:
-        """``out = silu(x Wg^T) * (x Wu^T)`` for a matrix whose rows interleave gate and
-        up in groups of ``group``.  Few bfloat16 rows: one kernel with the product in
-        its epilogue; otherwise the product, then the elementwise kernel."""
+    def linear_swiglu(self, x: torch.Tensor, w_gu: torch.Tensor, group: int, out: torch.Tensor,
+                      act: str = "silu") -> torch.Tensor:
+        """``out = act(x Wg^T) * (x Wu^T)`` for a matrix whose rows interleave gate and
+        up in groups of ``group``; ``act`` is ``"silu"`` or ``"gelu_tanh"``.  Few bfloat16 rows: one
+        kernel with the product in its epilogue; otherwise the product, then the elementwise kernel."""
         if group == 8 and w_gu.shape[0] % 16 == 0 and self._skinny(x, w_gu):
-            ops.stream_linear(x, w_gu, out, swiglu=True)
+            ops.stream_linear(x, w_gu, out, swiglu=True, act=act)
             return out
-        if group == 8 and w_gu.shape[0] % 16 == 0 and self._mid(x, w_gu):
+        if group == 8 and w_gu.shape[0] % 16 == 0 and act == "silu" and self._mid(x, w_gu):
             ops.mid_linear(x, w_gu, out, self.buffer("mid.partials", (ops.mid_rows_scratch(x.shape[0]),), torch.float32),
                            swiglu=True)
             return out
         own = self.gemm_backend == "tcgen05" or (self.gemm_backend == "auto"
                                                  and x.shape[0] >= self.fused_swiglu_min_rows)
         if own and group == 8 and w_gu.shape[0] % 16 == 0 and ops.gemm_ok(x, w_gu):
-            ops.gemm_bf16(x, w_gu, out, swiglu=True)
+            ops.gemm_bf16(x, w_gu, out, swiglu=True, act=act)
             return out
         gu = self.linear(x, w_gu, self.buffer("ffn.gu", (x.shape[0], w_gu.shape[0])))
-        ops.swiglu(gu, out, group)
+        ops.swiglu(gu, out, group, act)
         return out

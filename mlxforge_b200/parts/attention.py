@@ -16,7 +16,7 @@ from typing import Dict
 import torch
 
 from ..csrc import ops
-from .base import POSITIONS, Mixer, PagedKV, TensorSpec, build_part, register_mixer
+from .base import POSITIONS, Mixer, PagedKV, PartSpec, TensorSpec, build_part, register_mixer
 
 
 def paged_attention(rt, batch, q, lane, out, n_heads: int, scale: float, window: int) -> None:
@@ -119,3 +119,109 @@ class AttentionMixer(Mixer):
         qkv = self.project(x)
         q = self.encode_and_store(qkv, batch, cache, writes_cache)
         return self.output(self.attend(q, batch, cache))
+
+
+def sink_paged_attention(rt, batch, q, lane, out, m, gate, gate_ld: int) -> None:
+    """Attention with the options of ``SinkAttention`` (kept first keys, a sink, a gate on the output).
+    bfloat16 with head sizes the tensor-core kernels take: sequences that bring one token go to the
+    split-key decode kernel, portions of prompts to the prefill kernel; the 32-bit path and other
+    sizes take the block-per-token kernel."""
+    need = lane.need
+    table = batch.block_table(lane.group)
+    ops.attention_generic_ex(q, lane.k, lane.v, out, batch.positions, batch.seq_of_token, table, lane.page_size,
+                             m.n_heads, need.n_kv_heads, need.head_dim, m.scale, m.window, need.value_dim,
+                             need.head_dim if need.values_in_keys else need.value_dim, m.keep_first, m.sink, gate,
+                             gate_ld)
+
+
+_SINK_NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "sink": "sink"}
+
+
+@register_mixer("sink_attention")
+class SinkAttention(AttentionMixer):
+    """Grouped-query attention with four options, each a parameter:
+
+    * ``values``: ``"keys"`` — there is no value projection; the values are the keys as projected,
+      before the rotation (the value pages are filled beside the key pages) — or ``"own"``;
+    * ``window`` with ``keep_first``: query i sees key j if ``j <= i`` and (``i - j < window`` or
+      ``j < keep_first``); the kept keys stay at their own positions;
+    * ``sink``: a learned number per query head whose exponential joins the softmax denominator; it has
+      no key and no value and is not scaled;
+    * ``gate``: the concatenated heads are multiplied by ``sigmoid(Wg x)`` before the output projection.
+
+    All projections that read the mixer's input are one product.  ``names`` maps the tensors' roles to
+    their names behind the prefix."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, runtime):
+        p = dict(params)
+        p.setdefault("position", PartSpec("none", {"head_dim": int(p["head_dim"])}))
+        Mixer.__init__(self, p, prefix, runtime)
+        self.hidden = int(p["hidden_size"])
+        self.n_heads = int(p["n_heads"])
+        self.n_kv = int(p["n_kv_heads"])
+        self.hd = int(p["head_dim"])
+        self.scale = float(p["softmax_scale"])
+        self.window = int(p.get("window", 0) or 0)
+        self.keep_first = int(p.get("keep_first", 0) or 0) if self.window else 0
+        self.values = str(p.get("values", "own"))
+        self.has_sink = bool(p.get("sink", False))
+        self.has_gate = bool(p.get("gate", False))
+        self.names = dict(_SINK_NAMES, **(p.get("names") or {}))
+        if self.values not in ("own", "keys"):
+            raise ValueError(f"sink_attention: values must be 'own' or 'keys', got '{self.values}'")
+        if self.n_kv <= 0 or self.n_heads % self.n_kv:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if self.window < 0 or self.keep_first < 0:
+            raise ValueError("sink_attention: window and keep_first must not be negative")
+        self.position = build_part(POSITIONS, p["position"], runtime)
+        self.w_in = self.w_o = self.sink = None
+
+    def _n(self, role: str) -> str:
+        return self.prefix + self.names[role]
+
+    def _roles(self):
+        return ("q", "k") + (("v",) if self.values == "own" else ()) + (("g",) if self.has_gate else ())
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        q, kv = self.n_heads * self.hd, self.n_kv * self.hd
+        rows = {"q": q, "k": kv, "v": kv, "g": q}
+        specs = {self._n(r): TensorSpec((rows[r], self.hidden)) for r in self._roles()}
+        specs[self._n("o")] = TensorSpec((self.hidden, q))
+        if self.has_sink:
+            specs[self._n("sink")] = TensorSpec((self.n_heads,), role="vector")
+        specs.update(self.position.tensor_specs())
+        return specs
+
+    def bind(self, tensors) -> None:
+        self.position.bind(tensors)
+        dt = self.rt.dtype
+        self.w_in = torch.cat([tensors[self._n(r)].to(dt) for r in self._roles()], dim=0).contiguous()
+        self.w_o = tensors[self._n("o")].to(dt).contiguous()
+        if self.has_sink:
+            self.sink = tensors[self._n("sink")].to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_in.numel() + self.w_o.numel()) * self.w_in.element_size()
+
+    def cache_need(self):
+        return PagedKV(self.n_kv, self.hd, self.window, keep_first=self.keep_first)
+
+    def project(self, x):
+        """[T, H] -> queries, keys, (values,) (gates) side by side."""
+        return self.rt.linear(x, self.w_in, self.rt.buffer("sattn.in", (x.shape[0], self.w_in.shape[0])))
+
+    def encode_and_store(self, proj, batch, cache, writes_cache: bool):
+        q = self.rt.buffer("sattn.q", (proj.shape[0], self.n_heads * self.hd))
+        self.position.rotate_and_store(proj, batch, q, cache, self.n_heads, self.n_kv, writes_cache,
+                                       values_from_keys=self.values == "keys", ld=proj.shape[1])
+        return q
+
+    def forward(self, x, batch, cache, writes_cache: bool = True):
+        proj = self.project(x)
+        q = self.encode_and_store(proj, batch, cache, writes_cache)
+        o = self.rt.buffer("sattn.o", (q.shape[0], self.n_heads * self.hd))
+        gate = proj[:, proj.shape[1] - self.n_heads * self.hd:] if self.has_gate else None
+        sink_paged_attention(self.rt, batch, q, cache, o, self, gate, proj.shape[1])
+        return self.rt.linear(o, self.w_o, self.rt.buffer("sattn.delta", (o.shape[0], self.hidden)))

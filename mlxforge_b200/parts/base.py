@@ -114,13 +114,18 @@ class PagedKV:
     given back.  ``chunk`` > 0 means a query only reads keys of its own chunk
     (``floor(j / chunk) == floor(i / chunk)``), so the pages before the chunk of the
     next query are given back too.  ``v_head_dim`` > 0: values have another size than
-    keys (0: the same)."""
+    keys (0: the same).  ``keep_first`` > 0 (with a window): the first ``keep_first``
+    positions stay visible to every later query, so their pages are never given back.
+    ``values_in_keys``: the values are the first ``v_head_dim`` channels of the keys; the lane
+    has no value pool of its own and ``lane.v`` is ``lane.k``."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
     chunk: int = 0
     v_head_dim: int = 0
+    keep_first: int = 0
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -139,6 +144,15 @@ class FixedState:
 
 
 CacheNeed = Union[PagedKV, FixedState, None]
+
+
+@dataclass(frozen=True)
+class DeltaPair:
+    """Two deltas that are both still to be added to the residual stream (the two branches of a
+    layer that runs them side by side); either may be None.  A norm that is handed one adds both."""
+
+    first: Any = None
+    second: Any = None
 
 
 # --------------------------------------------------------------------------- interfaces

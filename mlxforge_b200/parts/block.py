@@ -7,7 +7,7 @@ previous block's last delta as ``pending`` and hands its own on.
 """
 from __future__ import annotations
 
-from .base import Block, register_block
+from .base import Block, DeltaPair, register_block
 
 
 @register_block("prenorm")
@@ -56,3 +56,26 @@ class StreamPreNormBlock(Block):
             x = self.feed_forward_norm.add_forward(residual, pending, read=c.w_in if c is not None else None)
             pending = self._write(c, self.feed_forward.forward(x, batch))
         return residual, pending
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """Mixer and feed-forward side by side on the same residual, each behind a norm of its own:
+    ``h += mixer(norm1(h)) + feed_forward(norm2(h))``.  The two deltas travel on as one
+    ``DeltaPair``; the next layer's pair of norms (or the final norm) adds both in 32-bit in the
+    kernel that normalises.  A layer without a feed-forward has the mixer's branch only.  The
+    norms must be ``rmsnorm`` parts (``pair_forward``)."""
+
+    roles = ("mixer", "mixer_norm")
+
+    def __init__(self, by_role, runtime):
+        super().__init__(by_role, runtime)
+        if self.feed_forward is not None and self.feed_forward_norm is None:
+            raise ValueError("parallel: a feed-forward needs a feed_forward_norm")
+
+    def forward(self, residual, pending, batch, cache, writes_cache: bool = True):
+        x1, x2 = self.mixer_norm.pair_forward(residual, pending,
+                                              self.feed_forward_norm if self.feed_forward is not None else None)
+        d1 = self.mixer.forward(x1, batch, cache, writes_cache)
+        d2 = self.feed_forward.forward(x2, batch) if self.feed_forward is not None else None
+        return residual, DeltaPair(d1, d2)

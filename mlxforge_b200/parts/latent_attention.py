@@ -1,0 +1,133 @@
+"""Attention over a compressed latent: every token keeps one normed latent vector ``c`` [kv_rank]
+and one rotated key part ``r`` [rot_dim] that all heads share, instead of keys and values per head.
+
+    c_q = rmsnorm(W_dq x) ;  q_h = (n_h | p_h) = rows of W_uq c_q, ``dim`` plain and ``rot_dim`` rotated
+    (c' | r') = W_dkv x ;    c = rmsnorm(c') ;  r = rotate(r')         (kept in the cache, per token)
+    k_h = (W_uk,h c | r) ;   v_h = W_uv,h c
+    s_h = (n_h . W_uk,h c + rotate(p_h) . r) * softmax_scale ;  causal softmax ;  o_h = sum_j p_j v_h,j
+    out = W_o (concat_h(o_h) * sigmoid(W_g x))
+
+The engine never expands keys or values: ``n_h . (W_uk,h c) = (W_uk,h^T n_h) . c``, so the query of a
+head becomes ``(W_uk,h^T n_h | rotate(p_h))``, ``kv_rank + rot_dim`` wide, the cached rows are its
+keys, their first ``kv_rank`` channels its values (one key head shared by all query heads, no value
+pool), and ``W_uv,h`` is applied to the attended latent.  A layer with ``shares_cache`` has no
+``W_dkv``: it reads the lane of the layer it names in the schedule and writes nothing.
+
+The rotation is the half-split one over all ``rot_dim`` channels.  Norms, angles, scores and the
+softmax are 32-bit.  ``names`` maps the tensors' roles to their names behind the prefix.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..csrc import ops
+from .base import Mixer, PagedKV, TensorSpec, register_mixer
+from .rope import inverse_wavelengths
+
+_NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv",
+          "g": "g", "o": "o"}
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads = int(p["n_heads"])
+        self.dim = int(p["head_dim"])
+        self.rot = int(p["rot_dim"])
+        self.vdim = int(p.get("v_head_dim") or self.dim)
+        self.q_rank = int(p["q_rank"])
+        self.rank = int(p["kv_rank"])
+        self.scale = float(p["softmax_scale"])
+        self.eps = float(p["eps"])
+        self.has_gate = bool(p.get("gate", True))
+        self.shares_cache = bool(p.get("shares_cache", False))
+        self.names = dict(_NAMES, **(p.get("names") or {}))
+        if self.rot % 2:
+            raise ValueError(f"latent_attention: rot_dim must be even, got {self.rot}")
+        if min(self.n_heads, self.dim, self.vdim, self.q_rank, self.rank) <= 0 or self.rot < 0:
+            raise ValueError("latent_attention: sizes must be positive")
+        self.inv_f, inv_d = inverse_wavelengths(self.rot, float(p.get("rope_base", 10000.0)), runtime.device)
+        self.inv_d = inv_d if runtime.precise else None
+        self.w_in = self.w_uq = self.w_ukT = self.w_uv = self.w_o = self.q_norm = self.kv_norm = None
+
+    def _n(self, role: str) -> str:
+        return self.prefix + self.names[role]
+
+    @property
+    def kv_width(self) -> int:
+        return self.rank + self.rot
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        H, nh = self.hidden, self.n_heads
+        specs = {
+            self._n("dq"): TensorSpec((self.q_rank, H)),
+            self._n("dq_norm"): TensorSpec((self.q_rank,), role="vector"),
+            self._n("uq"): TensorSpec((nh * (self.dim + self.rot), self.q_rank)),
+            self._n("uk"): TensorSpec((nh * self.dim, self.rank)),
+            self._n("uv"): TensorSpec((nh * self.vdim, self.rank)),
+            self._n("o"): TensorSpec((H, nh * self.vdim)),
+        }
+        if not self.shares_cache:
+            specs[self._n("dkv")] = TensorSpec((self.kv_width, H))
+            specs[self._n("dkv_norm")] = TensorSpec((self.rank,), role="vector")
+        if self.has_gate:
+            specs[self._n("g")] = TensorSpec((nh * self.vdim, H))
+        return specs
+
+    def bind(self, tensors) -> None:
+        dt, f32 = self.rt.dtype, torch.float32
+        roles = ("dq",) + (() if self.shares_cache else ("dkv",)) + (("g",) if self.has_gate else ())
+        self.w_in = torch.cat([tensors[self._n(r)].to(dt) for r in roles], dim=0).contiguous()
+        self.w_uq = tensors[self._n("uq")].to(dt).contiguous()
+        # [heads, kv_rank, dim]: head h's key expansion, transposed, so that it maps a query to the latent
+        self.w_ukT = tensors[self._n("uk")].to(dt).view(self.n_heads, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = tensors[self._n("uv")].to(dt).view(self.n_heads, self.vdim, self.rank).contiguous()
+        self.w_o = tensors[self._n("o")].to(dt).contiguous()
+        self.q_norm = tensors[self._n("dq_norm")].to(f32).contiguous()
+        if not self.shares_cache:
+            self.kv_norm = tensors[self._n("dkv_norm")].to(f32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() for w in (self.w_in, self.w_uq, self.w_ukT, self.w_uv, self.w_o)) * self.w_in.element_size()
+
+    def cache_need(self):
+        return PagedKV(1, self.kv_width, v_head_dim=self.rank, values_in_keys=True)
+
+    def attend(self, q_full, batch, cache, out):
+        latent_paged_attention(self.rt, batch, q_full, cache, out, self)
+
+    def forward(self, x, batch, cache, writes_cache: bool = True):
+        rt, T, nh = self.rt, x.shape[0], self.n_heads
+        proj = rt.linear(x, self.w_in, rt.buffer("lat.in", (T, self.w_in.shape[0])))
+        cq = rt.buffer("lat.cq", (T, self.q_rank))
+        ops.latent_prepare(proj, self.q_rank, self.q_rank, self.rank, self.rot, self.q_norm, self.kv_norm, self.eps,
+                           batch.positions, batch.seq_of_token, batch.block_table(cache.group), cache.page_size,
+                           self.inv_f, self.inv_d, cq, cache.k, writes_cache and not self.shares_cache)
+        q = rt.linear(cq, self.w_uq, rt.buffer("lat.q", (T, nh * (self.dim + self.rot))))
+        q_full = rt.buffer("lat.q_full", (T, nh * self.kv_width))
+        rt.head_linear(q, nh * (self.dim + self.rot), self.dim + self.rot, self.w_ukT, q_full, nh * self.kv_width,
+                       self.kv_width, T)
+        ops.latent_query(q, nh, self.dim, self.rot, self.rank, batch.positions, self.inv_f, self.inv_d, q_full)
+        o_lat = rt.buffer("lat.o_lat", (T, nh * self.rank))
+        self.attend(q_full, batch, cache, o_lat)
+        o = rt.buffer("lat.o", (T, nh * self.vdim))
+        gate = proj[:, proj.shape[1] - nh * self.vdim:] if self.has_gate else None
+        rt.head_linear(o_lat, nh * self.rank, self.rank, self.w_uv, o, nh * self.vdim, self.vdim, T, gate,
+                       proj.shape[1])
+        return rt.linear(o, self.w_o, rt.buffer("lat.delta", (T, self.hidden)))
+
+
+def latent_paged_attention(rt, batch, q, lane, out, m: LatentAttention) -> None:
+    """Causal attention of queries ``kv_rank + rot_dim`` wide over the lane's one key head, the values
+    being the keys' first ``kv_rank`` channels."""
+    need = lane.need
+    ops.attention_generic_ex(q, lane.k, lane.k, out, batch.positions, batch.seq_of_token,
+                             batch.block_table(lane.group), lane.page_size, m.n_heads, 1, need.head_dim, m.scale, 0,
+                             need.value_dim, need.head_dim)

@@ -1,6 +1,10 @@
 """RMSNorm: ``x * rsqrt(mean(x^2) + eps) * w`` over the last axis, the weight
 multiplying directly (src/model/decoder_model.cpp:206-208).  The sum of squares,
-the scaling and the residual sum it is fused with are 32-bit."""
+the scaling and the residual sum it is fused with are 32-bit.
+
+A layer whose branches run side by side on one residual hands on two deltas at once
+(``DeltaPair``) and wants two norms of the same sum: ``RMSNorm.pair_forward`` adds both deltas
+and applies both weights in one kernel."""
 from __future__ import annotations
 
 from typing import Dict
@@ -8,7 +12,7 @@ from typing import Dict
 import torch
 
 from ..csrc import ops
-from .base import Norm, TensorSpec, register_norm
+from .base import DeltaPair, Norm, TensorSpec, register_norm
 
 
 @register_norm("rmsnorm")
@@ -19,13 +23,14 @@ class RMSNorm(Norm):
         super().__init__(params, prefix, runtime)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.name = self.prefix + str(params.get("tensor", "weight"))
         self.weight = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {self.prefix + "weight": TensorSpec((self.size,), role="vector")}
+        return {self.name: TensorSpec((self.size,), role="vector")}
 
     def bind(self, tensors) -> None:
-        self.weight = tensors[self.prefix + "weight"].to(torch.float32).contiguous()
+        self.weight = tensors[self.name].to(torch.float32).contiguous()
 
     def weight_bytes(self) -> int:
         return self.size * 4
@@ -37,8 +42,24 @@ class RMSNorm(Norm):
         n = residual.shape[0] if rows is None else rows.shape[0]
         if out is None:
             out = self.rt.buffer("norm.out", (n, self.size))
-        ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
+        if isinstance(delta, DeltaPair):
+            ops.add_rmsnorm_pair(residual, delta.first, delta.second, self.weight, None, self.eps, out, None, rows)
+        else:
+            ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
         return out
+
+    def pair_forward(self, residual, delta, other: "RMSNorm" = None):
+        """``residual += delta`` (a tensor, a ``DeltaPair`` or None), then this norm of the sum and, with
+        ``other``, that norm (same size and eps, its own weight) of the same sum: (out, out_other)."""
+        if other is not None and (other.size != self.size or other.eps != self.eps):
+            raise ValueError("pair_forward: the two norms must agree in size and eps")
+        pair = delta if isinstance(delta, DeltaPair) else DeltaPair(delta, None)
+        n = residual.shape[0]
+        out1 = self.rt.buffer("norm.out", (n, self.size))
+        out2 = self.rt.buffer("norm.out2", (n, self.size)) if other is not None else None
+        ops.add_rmsnorm_pair(residual, pair.first, pair.second, self.weight, other.weight if other is not None else None,
+                             self.eps, out1, out2)
+        return out1, out2
 
 
 @register_norm("group_rmsnorm")

@@ -9,6 +9,13 @@ into their pages, so the encoding owns that step of the mixer.
 
 ``"none"`` is the encoding without positions: the same kernel with nothing
 rotated.
+
+``"rotary"`` is the plain rotation with its constants as parameters: ``base``, how many leading
+channels of a head rotate (``rotary_dim``) and the pairing (``"half"``: channel i with
+i + rotary_dim/2; ``"pairs"``: channel 2i with 2i + 1).  Pair i turns by
+``position * base^(-2i/rotary_dim)``; the angle is a 32-bit product on the bfloat16 path and a
+double one on the 32-bit path.  It can also fill the value pages with the keys as they were
+before the rotation, for mixers whose values are their keys.
 """
 from __future__ import annotations
 
@@ -79,3 +86,37 @@ class NoPositions(PositionEncoding):
         ops.rope_kv_write(qkv, batch.positions, batch.seq_of_token, batch.block_table(lane.group),
                           lane.page_size, None, q_out, lane.k, lane.v, n_heads, n_kv_heads,
                           self.head_dim, 0, writes_cache, self.rt.precise)
+
+
+def inverse_wavelengths(rotary_dim: int, base: float, device):
+    """``base^(-2i/rotary_dim)``, i < rotary_dim/2, worked out in double: (float32 tensor, float64 tensor)."""
+    if rotary_dim < 0 or rotary_dim % 2:
+        raise ValueError(f"rotary_dim must be even and not negative, got {rotary_dim}")
+    i = np.arange(rotary_dim // 2, dtype=np.float64)
+    inv = np.power(float(base), -2.0 * i / max(rotary_dim, 1))
+    return (torch.from_numpy(inv.astype(np.float32)).to(device), torch.from_numpy(inv).to(device))
+
+
+@register_position("rotary")
+class Rotary(PositionEncoding):
+    graph_safe = True
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.head_dim = int(params["head_dim"])
+        self.rotary_dim = int(params.get("rotary_dim", self.head_dim))
+        self.pairing = str(params.get("pairing", "half"))
+        if self.pairing not in ("half", "pairs"):
+            raise ValueError(f"rotary: pairing must be 'half' or 'pairs', got '{self.pairing}'")
+        if self.rotary_dim > self.head_dim:
+            raise ValueError("rotary_dim exceeds head_dim")
+        self.inv_f, inv_d = inverse_wavelengths(self.rotary_dim, float(params["base"]), runtime.device)
+        self.inv_d = inv_d if runtime.precise else None      # the 32-bit path takes its angles in double
+
+    def rotate_and_store(self, qkv, batch, q_out, lane, n_heads, n_kv_heads, writes_cache, values_from_keys=False,
+                         ld=None):
+        """``values_from_keys``: the rows hold queries and keys only, and the value pages get the keys as
+        projected.  ``ld``: elements between rows of ``qkv`` (it may hold further columns behind the heads)."""
+        ops.rope_store(qkv, batch.positions, batch.seq_of_token, batch.block_table(lane.group), lane.page_size,
+                       self.inv_f, self.inv_d, q_out, lane.k, lane.v, n_heads, n_kv_heads, self.head_dim,
+                       self.rotary_dim, self.pairing == "pairs", writes_cache, values_from_keys, ld)

@@ -248,9 +248,9 @@ def test_spec_declares_exactly_the_checkpoint_tensors_and_random_mode_lists_them
         get_architecture("Notirax").build_spec(config_from_json(json.loads(json.dumps(NX_A))))
 
 
-def test_unknown_architecture_lists_both_registered():
+def test_unknown_architecture_lists_the_registered():
     from mlxforge_b200.config import ConfigError, config_from_json
-    with pytest.raises(ConfigError, match="LlamaForCausalLM, Notirax"):
+    with pytest.raises(ConfigError, match="LlamaForCausalLM, Luzinex, Notirax"):
         config_from_json({"architecture": "Nothing"})
 
 
