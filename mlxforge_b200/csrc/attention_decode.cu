@@ -59,7 +59,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ v_pool, float* __restrict__ part_o,
                    float* __restrict__ part_ml, const int* __restrict__ positions,
                    const int* __restrict__ seq_of_token, PagedView pv, int n_heads, float scale_log2,
-                   int window, int max_splits) {
+                   int window, int max_splits, AttnOptions opt) {
   constexpr int KPW = Tile<HD_MAX>::KPW;
   constexpr int WARPS = Tile<HD_MAX>::W;
   constexpr int TILE = KPW * WARPS;
@@ -67,6 +67,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   constexpr int DT = HD_MAX / 8;        // output n-tiles (channels / 8)
   constexpr int KS = HD_MAX / 16;       // k-steps of the score product
   const int hd = pv.head_dim;
+  const int vd = opt.vd > 0 ? opt.vd : hd;
+  const bool v_in_k = opt.v_in_k != 0;
   const int ld = hd + 8;                // padded row: conflict-free ldmatrix for every hd % 16 == 0
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [16][ld]
@@ -83,9 +85,12 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int pos = positions[t], seq = seq_of_token[t];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int k_begin = split * SPLIT_KEYS;
-  if (k_begin > pos || k_begin + SPLIT_KEYS <= lo) return;       // nothing visible in this split
+  // keys below `keep` stay visible before the window (a split that holds some walks from its start)
+  const int keep = (window > 0 && opt.keep_first > 0) ? min(opt.keep_first, lo) : 0;
+  if (k_begin > pos || (k_begin + SPLIT_KEYS <= lo && k_begin >= keep)) return;   // nothing visible in this split
   // tiles of this split that hold visible keys
-  const int tile0 = max(k_begin, lo) / TILE, tile1 = min(k_begin + SPLIT_KEYS - 1, pos) / TILE;
+  const int tile0 = (k_begin < keep ? k_begin : max(k_begin, lo)) / TILE;
+  const int tile1 = min(k_begin + SPLIT_KEYS - 1, pos) / TILE;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunks = hd >> 3;            // 16-byte pieces per row
@@ -98,15 +103,26 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     long long gran_off = 0;
     {
       const int key16 = w_begin + lane * 16;
-      if (lane < KPW / 16 && key16 <= pos && key16 + 16 > lo) gran_off = granule_offset(pv, seq, key16, kvh);
+      if (lane < KPW / 16 && key16 <= pos && (key16 + 16 > lo || key16 < keep))
+        gran_off = granule_offset(pv, seq, key16, kvh);
     }
     for (int i = lane; i < KPW * chunks; i += 32) {
       const int r = i / chunks, c = i - r * chunks;
       const int key = w_begin + r;
-      const bool valid = key >= lo && key <= pos;
+      const bool valid = key <= pos && (key >= lo || key < keep);
       const long long off = __shfl_sync(0xffffffffu, gran_off, r >> 4) + (r & 15) * hd + c * 8;
       cp_async_16(k_s + r * ld + c * 8, k_pool + (valid ? off : 0), valid);
-      cp_async_16(v_s + r * ld + c * 8, v_pool + (valid ? off : 0), valid);
+      if (!v_in_k && vd == hd) cp_async_16(v_s + r * ld + c * 8, v_pool + (valid ? off : 0), valid);
+    }
+    if (!v_in_k && vd != hd) {             // value rows of their own width: same row of the pool, vd apart
+      const int vchunks = vd >> 3;
+      for (int i = lane; i < KPW * vchunks; i += 32) {
+        const int r = i / vchunks, c = i - r * vchunks;
+        const int key = w_begin + r;
+        const bool valid = key <= pos && (key >= lo || key < keep);
+        const long long off = __shfl_sync(0xffffffffu, gran_off, r >> 4) / hd * vd + (r & 15) * vd + c * 8;
+        cp_async_16(v_s + r * ld + c * 8, v_pool + (valid ? off : 0), valid);
+      }
     }
   };
 
@@ -144,9 +160,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       __syncwarp();                      // keys and values of a tile are the warp's own
     }
     const __nv_bfloat16* k_s = kv_s + ((stage * WARPS + warp) * 2 + 0) * KPW * ld;
-    const __nv_bfloat16* v_s = k_s + KPW * ld;
+    const __nv_bfloat16* v_s = v_in_k ? k_s : k_s + KPW * ld;
     const int w_begin = tile * TILE + warp * KPW;
-    if (w_begin <= pos && w_begin + KPW > lo) {
+    if (w_begin <= pos && (w_begin + KPW > lo || w_begin < keep)) {
       // ---- scores S[16 x KPW] = Q K^T
       float s[NT][4];
 #pragma unroll
@@ -174,7 +190,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
           float v = s[j][e] * scale_log2;
           if (edge) {
             const int key = w_begin + j * 8 + tq * 2 + (e & 1);
-            if (key < lo || key > pos) v = -INFINITY;
+            if ((key < lo && key >= keep) || key > pos) v = -INFINITY;
           }
           s[j][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -221,7 +237,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
         for (int d = 0; d < DT; d += 2) {
-          if (d * 8 < hd) {
+          if (d * 8 < vd) {
             unsigned b[4];
             const int mi = lane >> 3, r = lane & 7;
             ldmatrix_x4_trans(b, v_s + (kk * 16 + (mi & 1) * 8 + r) * ld + d * 8 + (mi >> 1) * 8);
@@ -248,7 +264,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   }
 #pragma unroll
   for (int d = 0; d < DT; d++) {
-    if (d * 8 < hd) {
+    if (d * 8 < vd) {
       float* r0 = o_s + (warp * 16 + g) * lo_s + d * 8 + tq * 2;
       float* r1 = o_s + (warp * 16 + g + 8) * lo_s + d * 8 + tq * 2;
       *reinterpret_cast<float2*>(r0) = make_float2(o[d][0], o[d][1]);
@@ -256,8 +272,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < n_rows * hd; i += WARPS * 32) {
-    const int r = i / hd, d = i - r * hd;
+  for (int i = threadIdx.x; i < n_rows * vd; i += WARPS * 32) {
+    const int r = i / vd, d = i - r * vd;
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < WARPS; w++) M = fmaxf(M, ml_s[(w * 16 + r) * 2]);
@@ -270,7 +286,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       acc += o_s[(w * 16 + r) * lo_s + d] * f;
     }
     const long long row = ((long long)t * n_heads + head0 + r) * max_splits + split;
-    part_o[row * hd + d] = acc;
+    part_o[row * vd + d] = acc;
     if (d == 0) {
       part_ml[row * 2 + 0] = M;
       part_ml[row * 2 + 1] = L;
@@ -278,42 +294,58 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   }
 }
 
-// One block per (token, head): merge the partials of the splits that saw keys.
+// One block per (token, head): merge the partials of the splits that saw keys.  `hd` is the width of
+// an output row.  With kept first keys the splits that hold some of them count beside the window's;
+// a sink joins the denominator here; a gate multiplies the result.
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, const int* __restrict__ positions,
-                                         int n_heads, int hd, int window, int max_splits, int split_keys) {
+                                         int n_heads, int hd, int window, int max_splits, int split_keys,
+                                         AttnOptions opt) {
   pdl_wait();
   pdl_launch();
   const int t = blockIdx.x, h = blockIdx.y;
   const int pos = positions[t];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int s0 = lo / split_keys, s1 = pos / split_keys, n = s1 - s0 + 1;
-  const long long row = ((long long)t * n_heads + h) * max_splits + s0;
+  const int keep = (window > 0 && opt.keep_first > 0) ? min(opt.keep_first, lo) : 0;
+  const int s0 = lo / split_keys, s1 = pos / split_keys;
+  // splits [0, k1) hold kept keys before the window's first split; then [s0, s1]
+  const int k1 = keep > 0 ? min((keep - 1) / split_keys + 1, s0) : 0;
+  const int n = k1 + s1 - s0 + 1;
+  const long long row0 = ((long long)t * n_heads + h) * max_splits;
+  auto row_of = [&](int i) { return row0 + (i < k1 ? i : s0 + (i - k1)); };
   // every warp works out the same weights, a split per lane: w_s = 2^(m_s - M) / L, so that the
   // loads of the splits' statistics go out together and not one after the other
   const int lane = threadIdx.x & 31;
+  const float sink = opt.sink ? opt.sink[h] * 1.4426950408889634f : -INFINITY;
   float M = -INFINITY;
-  for (int s = lane; s < n; s += 32) M = fmaxf(M, part_ml[(row + s) * 2]);
-  M = warp_max(M);
+  for (int s = lane; s < n; s += 32) M = fmaxf(M, part_ml[row_of(s) * 2]);
+  M = fmaxf(warp_max(M), sink);
   float L = 0.f;
-  for (int s = lane; s < n; s += 32) L += part_ml[(row + s) * 2 + 1] * exp2f(part_ml[(row + s) * 2] - M);
+  for (int s = lane; s < n; s += 32) L += part_ml[row_of(s) * 2 + 1] * exp2f(part_ml[row_of(s) * 2] - M);
   L = warp_sum(L);
+  if (opt.sink) L += exp2f(sink - M);
   const float inv = 1.0f / L;
+  const __nv_bfloat16* grow = opt.gate ? opt.gate + (long long)t * opt.gate_ld + (long long)h * hd : nullptr;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.f;
     int s = 0;
-    for (; s + 4 <= n; s += 4) {
-      const float o0 = part_o[(row + s) * hd + d], o1 = part_o[(row + s + 1) * hd + d];
-      const float o2 = part_o[(row + s + 2) * hd + d], o3 = part_o[(row + s + 3) * hd + d];
-      const float m0 = part_ml[(row + s) * 2], m1 = part_ml[(row + s + 1) * 2];
-      const float m2 = part_ml[(row + s + 2) * 2], m3 = part_ml[(row + s + 3) * 2];
+    for (; s + 4 <= n; s += 4) {         // four splits' loads go out together
+      const long long r0 = row_of(s), r1 = row_of(s + 1), r2 = row_of(s + 2), r3 = row_of(s + 3);
+      const float o0 = part_o[r0 * hd + d], o1 = part_o[r1 * hd + d];
+      const float o2 = part_o[r2 * hd + d], o3 = part_o[r3 * hd + d];
+      const float m0 = part_ml[r0 * 2], m1 = part_ml[r1 * 2], m2 = part_ml[r2 * 2], m3 = part_ml[r3 * 2];
       acc += o0 * exp2f(m0 - M);
       acc += o1 * exp2f(m1 - M);
       acc += o2 * exp2f(m2 - M);
       acc += o3 * exp2f(m3 - M);
     }
-    for (; s < n; s++) acc += part_o[(row + s) * hd + d] * exp2f(part_ml[(row + s) * 2] - M);
-    out[((long long)t * n_heads + h) * hd + d] = __float2bfloat16_rn(acc * inv);
+    for (; s < n; s++) {
+      const long long r = row_of(s);
+      acc += part_o[r * hd + d] * exp2f(part_ml[r * 2] - M);
+    }
+    acc *= inv;
+    if (grow) acc *= 1.0f / (1.0f + __expf(-__bfloat162float(grow[d])));
+    out[((long long)t * n_heads + h) * hd + d] = __float2bfloat16_rn(acc);
   }
 }
 
@@ -321,7 +353,7 @@ template <int HD_MAX>
 int launch_decode(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
                   __nv_bfloat16* out, float* part_o, float* part_ml, int n_tokens, int n_heads, PagedView pv,
                   const int* positions, const int* seq_of_token, float scale, int window, int max_ctx,
-                  cudaStream_t stream) {
+                  AttnOptions opt, cudaStream_t stream) {
   constexpr int KPW = Tile<HD_MAX>::KPW;
   constexpr int WARPS = Tile<HD_MAX>::W;
   constexpr int SPLIT = SPLIT_KEYS;
@@ -347,12 +379,14 @@ int launch_decode(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __n
   mf_count(MF_K_ATTN_DECODE);
   mf_count(MF_K_ATTN_DECODE_MERGE);
   cudaError_t e = launch_dep(attn_decode_kernel<HD_MAX>, grid, dim3(WARPS * 32), smem, stream, q, k_pool, v_pool,
-                             part_o, part_ml, positions, seq_of_token, pv, n_heads, scale * LOG2E, window, max_splits);
+                             part_o, part_ml, positions, seq_of_token, pv, n_heads, scale * LOG2E, window, max_splits,
+                             opt);
   if (e != cudaSuccess) return (int)e;
   dim3 mgrid(n_tokens, n_heads);
-  return (int)launch_dep(attn_decode_merge_kernel, mgrid, dim3(hd >= 128 ? 128 : 64), 0, stream,
-                         (const float*)part_o, (const float*)part_ml, out, positions, n_heads, hd, window, max_splits,
-                         SPLIT);
+  const int vd = opt.vd > 0 ? opt.vd : hd;
+  return (int)launch_dep(attn_decode_merge_kernel, mgrid, dim3(vd >= 128 ? 128 : 64), 0, stream,
+                         (const float*)part_o, (const float*)part_ml, out, positions, n_heads, vd, window, max_splits,
+                         SPLIT, opt);
 }
 
 }  // namespace
@@ -435,18 +469,45 @@ MF_API int mf_attention_decode_hinted(const void* q, const void* k_pool, const v
       const int max_splits = (max_ctx + split - 1) / split;
       dim3 mgrid(n_tokens, n_heads);
       return (int)launch_dep(attn_decode_merge_kernel, mgrid, dim3(hd), 0, stream, (const float*)part_o,
-                             (const float*)part_ml, oo, positions, n_heads, hd, window, max_splits, split);
+                             (const float*)part_ml, oo, positions, n_heads, hd, window, max_splits, split,
+                             AttnOptions{});
     }
     if (rc != MF_ERR_BAD_ARG) return rc;
   }
   if (hd <= 64)
     return launch_decode<64>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token, scale,
-                             window, max_ctx, stream);
+                             window, max_ctx, AttnOptions{}, stream);
   if (hd <= 128)
     return launch_decode<128>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token,
-                              scale, window, max_ctx, stream);
+                              scale, window, max_ctx, AttnOptions{}, stream);
   return launch_decode<256>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token, scale,
-                            window, max_ctx, stream);
+                            window, max_ctx, AttnOptions{}, stream);
+}
+
+// The same with the options of AttnOptions (value width, values inside the keys, kept first keys, sink,
+// output gate), always on the kernel without tensor copies and with the merge kernel after it.  `out`
+// and the gate are [n_tokens, n_heads * vd]; the scratch is sized as for mf_attention_decode.
+MF_API int mf_attention_decode_ex(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o,
+                                  float* part_ml, int n_tokens, int n_heads, int n_kv, int hd, const int* positions,
+                                  const int* seq_of_token, const int* block_table, int bt_stride, int page_size,
+                                  float scale, int window, int max_ctx, int vd, int v_in_k, int keep_first,
+                                  const float* sink, const void* gate, long long gate_ld, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (hd < 16 || hd > 256 || hd % 16 || n_kv <= 0 || n_heads % n_kv || max_ctx <= 0) return MF_ERR_BAD_ARG;
+  if (vd <= 0 || vd > hd || vd % 16 || keep_first < 0 || n_tokens > 65535) return MF_ERR_BAD_ARG;
+  PagedView pv{block_table, bt_stride, page_size, n_kv, hd};
+  const AttnOptions opt{vd, v_in_k, keep_first, sink, (const __nv_bfloat16*)gate, gate_ld};
+  const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_pool,
+                      *vv = (const __nv_bfloat16*)v_pool;
+  __nv_bfloat16* oo = (__nv_bfloat16*)out;
+  if (hd <= 64)
+    return launch_decode<64>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token, scale,
+                             window, max_ctx, opt, stream);
+  if (hd <= 128)
+    return launch_decode<128>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token,
+                              scale, window, max_ctx, opt, stream);
+  return launch_decode<256>(qq, kk, vv, oo, part_o, part_ml, n_tokens, n_heads, pv, positions, seq_of_token, scale,
+                            window, max_ctx, opt, stream);
 }
 
 MF_API int mf_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_o,

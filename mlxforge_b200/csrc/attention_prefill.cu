@@ -66,11 +66,13 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
                     const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                     const int* __restrict__ seq_ctx_len, int table_row0, PagedView pv, int n_heads,
-                    float scale_log2, int window) {
+                    float scale_log2, int window, AttnOptions opt) {
   constexpr int DT = HD_MAX / 8;
   constexpr int MT = Shape<HD_MAX>::MT;
   constexpr int BM = WARPS * 16 * MT;                          // queries per block
   const int hd = pv.head_dim, ld = hd + 8, chunks = hd >> 3;
+  const int vd = opt.vd > 0 ? opt.vd : hd, vchunks = vd >> 3;
+  const bool v_in_k = opt.v_in_k != 0;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [BM][ld]
   __nv_bfloat16* kv_s = q_s + BM * ld;                                    // [2 stages][K, V][BN][ld]
@@ -88,6 +90,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int pos_first = p0 + tile * BM, pos_last = pos_first + rows - 1;
   const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
   const int kt0 = lo_first / BN, kt1 = pos_last / BN;      // key tiles [kt0, kt1]
+  // keys kept visible before the window of this block's first query: their tiles come first
+  const int keep = (window > 0 && opt.keep_first > 0) ? min(opt.keep_first, lo_first) : 0;
+  const int n_keep = keep > 0 ? min((keep - 1) / BN + 1, kt0) : 0;
+  const int n_tiles = n_keep + kt1 - kt0 + 1;
+  auto tile_of = [&](int i) { return i < n_keep ? i : kt0 + (i - n_keep); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
 
@@ -98,15 +105,25 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     long long gran_off = 0;
     {
       const int key16 = kt * BN + lane * 16;
-      if (lane < BN / 16 && key16 <= pos_last && key16 + 16 > lo_first) gran_off = granule_offset(pv, seq_row, key16, kvh);
+      if (lane < BN / 16 && key16 <= pos_last && (key16 + 16 > lo_first || key16 < keep))
+        gran_off = granule_offset(pv, seq_row, key16, kvh);
     }
     for (int i = threadIdx.x; i < BN * chunks; i += WARPS * 32) {
       const int r = i / chunks, c = i - r * chunks;
       const int key = kt * BN + r;
-      const bool valid = key >= lo_first && key <= pos_last;
+      const bool valid = key <= pos_last && (key >= lo_first || key < keep);
       const long long off = __shfl_sync(0xffffffffu, gran_off, r >> 4) + (r & 15) * hd + c * 8;
       cp_async_16(k_s + r * ld + c * 8, k_pool + (valid ? off : 0), valid);
-      cp_async_16(v_s + r * ld + c * 8, v_pool + (valid ? off : 0), valid);
+      if (!v_in_k && vd == hd) cp_async_16(v_s + r * ld + c * 8, v_pool + (valid ? off : 0), valid);
+    }
+    if (!v_in_k && vd != hd) {             // value rows of their own width: same row of the pool, vd apart
+      for (int i = threadIdx.x; i < BN * vchunks; i += WARPS * 32) {
+        const int r = i / vchunks, c = i - r * vchunks;
+        const int key = kt * BN + r;
+        const bool valid = key <= pos_last && (key >= lo_first || key < keep);
+        const long long off = __shfl_sync(0xffffffffu, gran_off, r >> 4) / hd * vd + (r & 15) * vd + c * 8;
+        cp_async_16(v_s + r * ld + c * 8, v_pool + (valid ? off : 0), valid);
+      }
     }
   };
 
@@ -117,20 +134,22 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     cp_async_16(q_s + r * ld + c * 8, q + ((long long)(q_start + tile * BM + rr) * n_heads + head) * hd + c * 8,
                 r < rows);
   }
-  load_kv(kt0, 0);
+  load_kv(tile_of(0), 0);
   cp_async_commit();
 
   // this warp's queries: MT tiles of 16 rows; thread rows g and g + 8 of each
   const int wrow0 = warp * 16 * MT;
   float m_row[MT][2], l_row[MT][2];
   float o[MT][DT][4];
+  // a sink is a key of score sink_h (not scaled) whose value is zero: the running maximum and sum start from it
+  const float m_init = opt.sink ? opt.sink[head] * LOG2E : -INFINITY, l_init = opt.sink ? 1.f : 0.f;
   int my_pos[MT][2], my_lo[MT][2];
 #pragma unroll
   for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
     for (int h = 0; h < 2; h++) {
-      m_row[mt][h] = -INFINITY;
-      l_row[mt][h] = 0.f;
+      m_row[mt][h] = m_init;
+      l_row[mt][h] = l_init;
       my_pos[mt][h] = pos_first + wrow0 + mt * 16 + g + h * 8;
       my_lo[mt][h] = (window > 0 && my_pos[mt][h] - window + 1 > 0) ? my_pos[mt][h] - window + 1 : 0;
     }
@@ -140,14 +159,15 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int w_pos_first = pos_first + wrow0, w_pos_last = w_pos_first + 16 * MT - 1;
   const int w_lo_last = (window > 0 && w_pos_last - window + 1 > 0) ? w_pos_last - window + 1 : 0;
 
-  for (int kt = kt0; kt <= kt1; kt++) {
-    const int stage = (kt - kt0) & 1;
-    if (kt < kt1) load_kv(kt + 1, stage ^ 1);
+  for (int ti = 0; ti < n_tiles; ti++) {
+    const int kt = tile_of(ti);
+    const int stage = ti & 1;
+    if (ti + 1 < n_tiles) load_kv(tile_of(ti + 1), stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();           // everything but the tile just requested has landed
     __syncthreads();
     const __nv_bfloat16* k_s = kv_s + (stage * 2 + 0) * BN * ld;
-    const __nv_bfloat16* v_s = kv_s + (stage * 2 + 1) * BN * ld;
+    const __nv_bfloat16* v_s = v_in_k ? k_s : kv_s + (stage * 2 + 1) * BN * ld;
 
     // a warp whose queries all lie before this key tile has nothing to do in it
     const bool active = kt * BN <= w_pos_last;
@@ -187,7 +207,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
             for (int e = 0; e < 4; e++) {
               const int key = kt * BN + j * 8 + tq * 2 + (e & 1);
-              if (key > my_pos[mt][e >> 1] || key < my_lo[mt][e >> 1]) sc[mt][j][e] = -INFINITY;
+              if (key > my_pos[mt][e >> 1] || (key < my_lo[mt][e >> 1] && key >= opt.keep_first))
+                sc[mt][j][e] = -INFINITY;
             }
       }
 #pragma unroll
@@ -244,7 +265,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         }
 #pragma unroll
         for (int d = 0; d < DT; d += 2) {
-          if (d * 8 < hd) {
+          if (d * 8 < vd) {
             unsigned b[4];
             const int mi = lane >> 3, r = lane & 7;
             ldmatrix_x4_trans(b, v_s + (kk * 16 + (mi & 1) * 8 + r) * ld + d * 8 + (mi >> 1) * 8);
@@ -269,12 +290,19 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       const int r = wrow0 + mt * 16 + g + h * 8;
       if (r >= rows) continue;
       const float inv = 1.0f / l_row[mt][h];
-      __nv_bfloat16* orow = out + ((long long)(q_start + tile * BM + r) * n_heads + head) * hd;
+      const long long trow = q_start + tile * BM + r;
+      __nv_bfloat16* orow = out + (trow * n_heads + head) * vd;
+      const __nv_bfloat16* grow = opt.gate ? opt.gate + trow * opt.gate_ld + (long long)head * vd : nullptr;
 #pragma unroll
       for (int d = 0; d < DT; d++) {
-        if (d * 8 < hd) {
-          *reinterpret_cast<unsigned*>(orow + d * 8 + tq * 2) =
-              pack_bf16(o[mt][d][h * 2] * inv, o[mt][d][h * 2 + 1] * inv);
+        if (d * 8 < vd) {
+          float o0 = o[mt][d][h * 2] * inv, o1 = o[mt][d][h * 2 + 1] * inv;
+          if (grow) {
+            const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(grow + d * 8 + tq * 2));
+            o0 *= 1.0f / (1.0f + __expf(-gg.x));
+            o1 *= 1.0f / (1.0f + __expf(-gg.y));
+          }
+          *reinterpret_cast<unsigned*>(orow + d * 8 + tq * 2) = pack_bf16(o0, o1);
         }
       }
     }
@@ -285,7 +313,7 @@ template <int HD_MAX>
 int launch_prefill(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __nv_bfloat16* v_pool,
                    __nv_bfloat16* out, const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
                    int table_row0, int n_seqs, int max_q_len, int n_heads, PagedView pv, float scale, int window,
-                   cudaStream_t stream) {
+                   AttnOptions opt, cudaStream_t stream) {
   constexpr int BM = WARPS * 16 * Shape<HD_MAX>::MT;
   const int ld = pv.head_dim + 8;
   const size_t smem = (size_t)(BM * ld + 4 * BN * ld) * sizeof(__nv_bfloat16);
@@ -304,7 +332,7 @@ int launch_prefill(const __nv_bfloat16* q, const __nv_bfloat16* k_pool, const __
   mf_count(MF_K_ATTN_PREFILL_MMA);
   attn_prefill_kernel<HD_MAX><<<grid, WARPS * 32, smem, stream>>>(q, k_pool, v_pool, out, seq_q_start, seq_q_len,
                                                                  seq_ctx_len, table_row0, pv, n_heads,
-                                                                 scale * LOG2E, window);
+                                                                 scale * LOG2E, window, opt);
   return (int)cudaGetLastError();
 }
 
@@ -338,12 +366,40 @@ MF_API int mf_attention_prefill(const void* q, const void* k_pool, const void* v
                                      max_q_len, n_tokens, n_heads, pv, scale, window, status, stream);
     if (rc != MF_ERR_BAD_ARG) return rc;
   }
+  const AttnOptions none{};
   if (hd <= 64)
     return launch_prefill<64>(qq, kk, vv, oo, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs, max_q_len,
-                              n_heads, pv, scale, window, stream);
+                              n_heads, pv, scale, window, none, stream);
   if (hd <= 128)
     return launch_prefill<128>(qq, kk, vv, oo, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs, max_q_len,
-                               n_heads, pv, scale, window, stream);
+                               n_heads, pv, scale, window, none, stream);
   return launch_prefill<256>(qq, kk, vv, oo, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs, max_q_len,
-                             n_heads, pv, scale, window, stream);
+                             n_heads, pv, scale, window, none, stream);
+}
+
+// The same with the options of AttnOptions (value width, values inside the keys, kept first keys, sink,
+// output gate), always on the mma.sync kernel.  `out` and the gate are [T, n_heads * vd].
+MF_API int mf_attention_prefill_ex(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                   const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
+                                   int table_row0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
+                                   const int* block_table, int bt_stride, int page_size, float scale, int window,
+                                   int vd, int v_in_k, int keep_first, const float* sink, const void* gate,
+                                   long long gate_ld, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0) return 0;
+  if (hd < 16 || hd > 256 || hd % 16 || n_kv <= 0 || n_heads % n_kv) return MF_ERR_BAD_ARG;
+  if (vd <= 0 || vd > hd || vd % 16 || keep_first < 0) return MF_ERR_BAD_ARG;
+  if (n_heads > 65535 || n_seqs > 65535) return MF_ERR_BAD_ARG;
+  PagedView pv{block_table, bt_stride, page_size, n_kv, hd};
+  const AttnOptions opt{vd, v_in_k, keep_first, sink, (const __nv_bfloat16*)gate, gate_ld};
+  const __nv_bfloat16 *qq = (const __nv_bfloat16*)q, *kk = (const __nv_bfloat16*)k_pool,
+                      *vv = (const __nv_bfloat16*)v_pool;
+  __nv_bfloat16* oo = (__nv_bfloat16*)out;
+  if (hd <= 64)
+    return launch_prefill<64>(qq, kk, vv, oo, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs, max_q_len,
+                              n_heads, pv, scale, window, opt, stream);
+  if (hd <= 128)
+    return launch_prefill<128>(qq, kk, vv, oo, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs, max_q_len,
+                               n_heads, pv, scale, window, opt, stream);
+  return launch_prefill<256>(qq, kk, vv, oo, seq_q_start, seq_q_len, seq_ctx_len, table_row0, n_seqs, max_q_len,
+                             n_heads, pv, scale, window, opt, stream);
 }

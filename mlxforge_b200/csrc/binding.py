@@ -82,6 +82,10 @@ _SIGNATURES = {
     "mf_moe_grouped_max_tiles": [c_int, c_int, c_int],
     "mf_moe_grouped_up": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, _P],
     "mf_moe_grouped_down": [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "mf_attention_prefill_ex": [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, c_int,
+                                c_float, c_int, c_int, c_int, c_int, _P, _P, c_longlong, _P],
+    "mf_attention_decode_ex": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,
+                               c_float, c_int, c_int, c_int, c_int, c_int, _P, _P, c_longlong, _P],
     "mf_gated_act": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "mf_add_rmsnorm_pair": [_P, _P, _P, c_int, _P, _P, c_float, _P, _P, c_int, _P, c_int, c_int, _P],
     "mf_attention_generic_ex": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, c_int,

@@ -87,6 +87,21 @@ __device__ __forceinline__ long long paged_offset(const PagedView& pv, int seq, 
   return ((page * pv.n_kv_heads + kv_head) * pv.page_size + slot) * (long long)pv.head_dim;
 }
 
+// Options of the tensor-core attention kernels beyond causal grouped-query attention with a window;
+// all off when zero.  vd: width of a value row (0: head_dim; at most head_dim).  v_in_k: the values
+// are the first vd channels of the keys (no value pool is read).  keep_first: with a window, keys at
+// positions below it stay visible to every later query.  sink: one float per query head whose
+// exponential joins the softmax denominator (unscaled; no key, no value).  gate: the output row
+// [n_heads * vd] is multiplied by sigmoid(gate[t * gate_ld + ...]).
+struct AttnOptions {
+  int vd;
+  int v_in_k;
+  int keep_first;
+  const float* sink;
+  const __nv_bfloat16* gate;
+  long long gate_ld;
+};
+
 // Offset of the first of 16 consecutive positions [pos16, pos16 + 16), pos16 a multiple
 // of 16: they share a page because the page size is a multiple of 16.  Rows of the
 // granule are head_dim apart.  Kernels look this up once per granule and not once per

@@ -147,6 +147,53 @@ def attention_generic_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                                             _ptr(gate), gate_ld, _stream()), "attention_generic")
 
 
+def attention_tc_ok(head_dim: int, v_dim: int, page_size: int) -> bool:
+    """Whether the tensor-core attention kernels with options take these sizes."""
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256 and v_dim % 16 == 0 and 0 < v_dim <= head_dim \
+        and page_size % 16 == 0
+
+
+def attention_prefill_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                         seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, seq_ctx_len: torch.Tensor,
+                         table_row0: int, max_q_len: int, block_table: torch.Tensor, page_size: int, n_heads: int,
+                         n_kv: int, head_dim: int, scale: float, window: int, v_dim: int, v_in_k: bool,
+                         keep_first: int = 0, sink: Optional[torch.Tensor] = None,
+                         gate: Optional[torch.Tensor] = None, gate_ld: int = 0) -> None:
+    """``attention_prefill`` with options: values ``v_dim`` wide (``v_in_k``: the first channels of the keys),
+    kept first keys, a sink per head, the output times sigmoid(``gate``).  bfloat16, the mma.sync kernel."""
+    _need_cuda(q, k_pool, v_pool, out, seq_q_start, seq_q_len, seq_ctx_len, block_table, sink)
+    if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill_ex: bfloat16 only")
+    check(library().mf_attention_prefill_ex(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+                                            seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_ctx_len.data_ptr(),
+                                            table_row0, seq_q_len.shape[0], max_q_len, n_heads, n_kv, head_dim,
+                                            block_table.data_ptr(), block_table.shape[1], page_size, scale, window,
+                                            v_dim, int(v_in_k), keep_first, _ptr(sink), _ptr(gate), gate_ld,
+                                            _stream()), "attention_prefill_ex")
+
+
+def attention_decode_ex(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                        part_o: torch.Tensor, part_ml: torch.Tensor, positions: torch.Tensor,
+                        seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int, n_heads: int,
+                        n_kv: int, head_dim: int, scale: float, window: int, max_ctx: int, v_dim: int, v_in_k: bool,
+                        keep_first: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                        gate_ld: int = 0) -> None:
+    """``attention_decode`` with the same options; scratch as ``attention_decode_scratch`` says."""
+    _need_cuda(q, k_pool, v_pool, out, part_o, part_ml, positions, seq_of_token, block_table, sink)
+    if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
+        raise KernelError("attention_decode_ex: bfloat16 only")
+    n = q.shape[0]
+    need_o, need_ml = attention_decode_scratch(n, n_heads, head_dim, max_ctx)
+    if part_o.numel() < need_o or part_ml.numel() < need_ml or part_o.dtype != torch.float32:
+        raise KernelError("attention_decode_ex: scratch too small")
+    check(library().mf_attention_decode_ex(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+                                           part_o.data_ptr(), part_ml.data_ptr(), n, n_heads, n_kv, head_dim,
+                                           positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+                                           block_table.shape[1], page_size, scale, window, max_ctx, v_dim,
+                                           int(v_in_k), keep_first, _ptr(sink), _ptr(gate), gate_ld, _stream()),
+          "attention_decode_ex", launches=2)
+
+
 def latent_prepare(proj: torch.Tensor, q_rank: int, kv_off: int, rank: int, rot: int, wq: torch.Tensor,
                    wkv: Optional[torch.Tensor], eps: float, positions: torch.Tensor, seq_of_token: torch.Tensor,
                    block_table: torch.Tensor, page_size: int, inv_f, inv_d, cq_out: torch.Tensor,

@@ -121,17 +121,33 @@ class AttentionMixer(Mixer):
         return self.output(self.attend(q, batch, cache))
 
 
-def sink_paged_attention(rt, batch, q, lane, out, m, gate, gate_ld: int) -> None:
-    """Attention with the options of ``SinkAttention`` (kept first keys, a sink, a gate on the output).
-    bfloat16 with head sizes the tensor-core kernels take: sequences that bring one token go to the
-    split-key decode kernel, portions of prompts to the prefill kernel; the 32-bit path and other
-    sizes take the block-per-token kernel."""
+def options_paged_attention(rt, batch, q, lane, out, n_heads: int, scale: float, window: int = 0, keep_first: int = 0,
+                            sink=None, gate=None, gate_ld: int = 0) -> None:
+    """Attention over ``lane`` with the options beyond a window: values of their own width or inside the
+    keys (the lane's need says which), kept first keys, a sink, a gate on the output.  bfloat16 with sizes
+    the tensor-core kernels take: the sequences that bring one token (the batch lays them out first) go to
+    the split-key decode kernel, portions of prompts to the prefill kernel; the 32-bit path and other sizes
+    take the block-per-token kernel."""
     need = lane.need
     table = batch.block_table(lane.group)
-    ops.attention_generic_ex(q, lane.k, lane.v, out, batch.positions, batch.seq_of_token, table, lane.page_size,
-                             m.n_heads, need.n_kv_heads, need.head_dim, m.scale, m.window, need.value_dim,
-                             need.head_dim if need.values_in_keys else need.value_dim, m.keep_first, m.sink, gate,
-                             gate_ld)
+    vd, in_k = need.value_dim, need.values_in_keys
+    if q.dtype != torch.bfloat16 or not ops.attention_tc_ok(need.head_dim, vd, lane.page_size):
+        ops.attention_generic_ex(q, lane.k, lane.v, out, batch.positions, batch.seq_of_token, table, lane.page_size,
+                                 n_heads, need.n_kv_heads, need.head_dim, scale, window, vd,
+                                 need.head_dim if in_k else vd, keep_first, sink, gate, gate_ld)
+        return
+    nd = batch.n_decode
+    if nd > 0:
+        n_o, n_ml = ops.attention_decode_scratch(nd, n_heads, need.head_dim, batch.max_ctx)
+        ops.attention_decode_ex(q[:nd], lane.k, lane.v, out[:nd], rt.buffer("attn.part_o", (n_o,), torch.float32),
+                                rt.buffer("attn.part_ml", (n_ml,), torch.float32), batch.positions[:nd],
+                                batch.seq_of_token[:nd], table, lane.page_size, n_heads, need.n_kv_heads,
+                                need.head_dim, scale, window, batch.max_ctx, vd, in_k, keep_first, sink, gate, gate_ld)
+    if nd < batch.n_tokens:
+        ops.attention_prefill_ex(q, lane.k, lane.v, out, batch.seq_q_start[nd:], batch.seq_q_len[nd:],
+                                 batch.seq_ctx_len[nd:], nd, max(batch.q_len[nd:]), table, lane.page_size, n_heads,
+                                 need.n_kv_heads, need.head_dim, scale, window, vd, in_k, keep_first, sink, gate,
+                                 gate_ld)
 
 
 _SINK_NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "sink": "sink"}
@@ -223,5 +239,6 @@ class SinkAttention(AttentionMixer):
         q = self.encode_and_store(proj, batch, cache, writes_cache)
         o = self.rt.buffer("sattn.o", (q.shape[0], self.n_heads * self.hd))
         gate = proj[:, proj.shape[1] - self.n_heads * self.hd:] if self.has_gate else None
-        sink_paged_attention(self.rt, batch, q, cache, o, self, gate, proj.shape[1])
+        options_paged_attention(self.rt, batch, q, cache, o, self.n_heads, self.scale, self.window, self.keep_first,
+                                self.sink, gate, proj.shape[1])
         return self.rt.linear(o, self.w_o, self.rt.buffer("sattn.delta", (o.shape[0], self.hidden)))

@@ -126,8 +126,6 @@ class LatentAttention(Mixer):
 
 def latent_paged_attention(rt, batch, q, lane, out, m: LatentAttention) -> None:
     """Causal attention of queries ``kv_rank + rot_dim`` wide over the lane's one key head, the values
-    being the keys' first ``kv_rank`` channels."""
-    need = lane.need
-    ops.attention_generic_ex(q, lane.k, lane.k, out, batch.positions, batch.seq_of_token,
-                             batch.block_table(lane.group), lane.page_size, m.n_heads, 1, need.head_dim, m.scale, 0,
-                             need.value_dim, need.head_dim)
+    being the keys' first ``kv_rank`` channels: the attention kernels' option ``values_in_keys``."""
+    from .attention import options_paged_attention
+    options_paged_attention(rt, batch, q, lane, out, m.n_heads, m.scale)
