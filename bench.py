@@ -481,6 +481,31 @@ def kernel_work(name, a, k, info):
     if name == "moe_rows":
         x, w_gu, ids = a[0], a[1], a[3]
         return (ids.numel() * 3 * w_gu.shape[2] * x.shape[1] * 2, 0, 0)
+    if name == "add_rmsnorm_pair":
+        resid, d1, d2, out1, out2 = a[0], a[1], a[2], a[6], a[7]
+        rows = a[8] if len(a) > 8 else k.get("rows")
+        n = out1.shape[0]
+        moved = n * resid.shape[1] * 4 * (2 if (d1 is not None or d2 is not None) and rows is None else 1)
+        return (moved + _nbytes(out1, out2) + sum(n * d.shape[1] * d.element_size() for d in (d1, d2) if d is not None), 0, 0)
+    if name in ("attention_prefill_ex", "attention_decode_ex"):
+        pre = name == "attention_prefill_ex"
+        H, n_kv, hd, window, vd, in_k = (a[11], a[12], a[13], a[15], a[16], a[17]) if pre else \
+            (a[10], a[11], a[12], a[14], a[16], a[17])
+        keep = (a[18] if len(a) > 18 else k.get("keep_first", 0)) if window else 0
+        if pre:
+            seen = sum(min(p + 1, window + keep) if window else p + 1 for p in range(T))
+            return (0, 2.0 * seen * H * (hd + vd), 0)
+        seen = info["seqs"] * (min(info["ctx"], window + keep) if window else info["ctx"])
+        return (seen * n_kv * (hd + (0 if in_k else vd)) * 2, 0, 0)
+    if name == "head_linear":
+        w, n_tok = a[3], a[7]
+        heads, n, kk = w.shape
+        return (_nbytes(w) + n_tok * heads * (n + kk) * w.element_size(), 2.0 * n_tok * heads * n * kk, 0)
+    if name == "retention_recurrence":
+        qk, state, o, nh, dim, vdim = a[0], a[4], a[6], a[7], a[8], a[9]
+        return (_nbytes(qk, o) + T * nh * vdim * 2 + 2 * info["seqs"] * nh * dim * vdim * 4, 0, 4.0 * T * nh * dim * vdim)
+    if name in ("rope_store", "latent_prepare", "latent_query", "retention_prepare", "retention_output"):
+        return (_nbytes(*[t for t in a if hasattr(t, "numel") and t.dim() >= 2 and t.numel() < (1 << 28)]), 0, 0)
     if name in ("gemm_bf16", "stream_linear"):
         x, w, out = a[0], a[1], a[2]
         return (_nbytes(x, w, out), 2.0 * x.shape[0] * w.shape[0] * w.shape[1], 0)
@@ -496,7 +521,7 @@ LLAMA_KERNELS = ("embed", "add_rmsnorm", "rope_kv_write", "attention_prefill", "
                  "stream_linear", "gemm_bf16")
 
 
-def kernel_table(engine, names, tokens, batch, ctx, chunk, pk):
+def kernel_table(engine, names, tokens, batch, ctx, chunk, pk, extra=None):
     """Per kind of kernel: microseconds per call in a prefill of `tokens` tokens and in a decode step of
     `batch` sequences at `ctx`, and the fraction of the roofline (the slowest of bytes / HBM copy,
     tensor FLOPs / the library's bfloat16 product and 32-bit FLOPs / the nominal FMA rate)."""
@@ -518,7 +543,7 @@ def kernel_table(engine, names, tokens, batch, ctx, chunk, pk):
         for n, calls in kt.measure().items():
             # the call whose time is the median of its kind stands for the kind, with its own work
             us, a, k = sorted(calls, key=lambda c: c[0])[len(calls) // 2]
-            b, tf, ff = kernel_work(n, a, k, info)
+            b, tf, ff = kernel_work(n, a, k, dict(info, **(extra or {})))
             roof = max(b / (pk["hbm_gbs"] * 1e9), tf / (pk["bf16_tflops"] * 1e12), ff / (FP32_TFLOPS_NOMINAL * 1e12)) * 1e6
             table[f"{phase}.{n}"] = {"us": round(us, 1), "calls": len(calls), "roof_us": round(roof, 2),
                                      "frac": round(roof / us, 3) if roof else None,
@@ -590,6 +615,91 @@ def run_notirax(args) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------- --workload luzinex
+# The Luzinex design at sizes that resemble a real model's layers, beside the closest existing model
+# (the Llama decoder) at equal size: the same width, layers, vocabulary and feed-forward width, the
+# heads and head size of its windowed attention layers.
+LUZINEX_SIZES = {
+    "s": dict(width=1024, layers=6, vocab=32768, ff=4096, heads=8, kv=2, dim=128, rot=64, window=1024, keep=4,
+              l_heads=8, l_dim=64, l_rot=32, l_vdim=64, q_rank=384, kv_rank=128, r_heads=8, r_dim=128, r_vdim=128,
+              context=4096),
+    "m": dict(width=2048, layers=6, vocab=32768, ff=8192, heads=16, kv=4, dim=128, rot=64, window=2048, keep=4,
+              l_heads=16, l_dim=64, l_rot=32, l_vdim=64, q_rank=768, kv_rank=192, r_heads=16, r_dim=128, r_vdim=128,
+              context=4096),
+}
+LUZINEX_KERNELS = ("embed", "add_rmsnorm_pair", "rope_store", "latent_prepare", "latent_query", "head_linear",
+                   "attention_prefill_ex", "attention_decode_ex", "attention_generic_ex", "retention_prepare",
+                   "retention_recurrence", "retention_chunked", "retention_output", "swiglu", "stream_linear", "gemm_bf16")
+
+
+def luzinex_config(z):
+    latent = {"heads": z["l_heads"], "dim": z["l_dim"], "rot_dim": z["l_rot"], "vdim": z["l_vdim"], "q_rank": z["q_rank"],
+              "kv_rank": z["kv_rank"], "scale": (z["l_dim"] + z["l_rot"]) ** -0.5, "rot": {"base": 500000.0, "dims": z["l_rot"]}}
+    attn = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+            "rot": {"base": 50000.0, "dims": z["rot"]}, "mask": {"size": z["window"], "keep_first": z["keep"]}}
+    ret = {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "rot": {"base": 1000000.0, "dims": z["r_dim"]},
+           "decay": [1.0 - 2.0 ** -(5 + 6.0 * h / z["r_heads"]) for h in range(z["r_heads"])]}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    layers = []
+    for i in range(z["layers"]):
+        kind = ("latent_attention", "attention", "retention")[i % 3]
+        mixer = dict(latent, **({"kv_from": 0} if i >= 3 else {})) if kind == "latent_attention" else \
+            dict(attn) if kind == "attention" else dict(ret)
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Luzinex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def luzinex_llama_like(z):
+    return dict(LLAMA_1B, num_hidden_layers=z["layers"], hidden_size=z["width"], num_attention_heads=z["heads"],
+                num_key_value_heads=z["kv"], head_dim=z["dim"], intermediate_size=z["ff"], vocab_size=z["vocab"],
+                rope_scaling=None, tie_word_embeddings=False)
+
+
+def run_luzinex(args) -> int:
+    import torch
+    import mlxforge_b200 as mf
+    from mlxforge_b200.config import config_from_json
+    from mlxforge_b200.csrc import ops
+    pk = peaks()
+    out = {"workload": "luzinex", "dtype": "bf16", "peaks": pk,
+           "data": "synthetic: seeded random weights, seeded uniform token ids, random cache contents",
+           "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1), "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for key in ([args.size] if args.size else sorted(LUZINEX_SIZES)):
+        z = LUZINEX_SIZES[key]
+        res = {"size": z}
+        for which, cfg_json, names in (("luzinex", luzinex_config(z), LUZINEX_KERNELS),
+                                       ("llama_equal_size", luzinex_llama_like(z), LLAMA_KERNELS)):
+            tmp = tempfile.mkdtemp(prefix="mlxforge_bench_")
+            try:
+                d = mf.write_random_model(os.path.join(tmp, "model"), config_from_json(cfg_json), seed=0, dtype="bfloat16")
+                engine = mf.Engine(model_spec=d, dtype="bfloat16", kv_pool_tokens=(args.batch + 2) * (z["context"] + 2048 + 64),
+                                   max_running=max(8, args.batch), token_budget=8192, prefill_chunk=2048)
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            for pool in set(engine.cache._k + engine.cache._v):
+                pool.normal_(0.0, 1.0)
+            ctx = z["context"]
+            t_pre = prefill_device(engine, PREFILL_TOKENS, runs=3, warmup=3)
+            sec, launches, _, _ = decode_device(engine, args.batch, ctx, args.steps, args.warmup)
+            r = {"prefill_tokens": PREFILL_TOKENS, "prefill_ms": round(t_pre * 1e3, 3),
+                 "prefill_tokens_per_s": round(PREFILL_TOKENS / t_pre, 1), "decode_batch": args.batch, "decode_context": ctx,
+                 "decode_ms_per_step": round(sec * 1e3, 4), "decode_tokens_per_s": round(args.batch / sec, 1),
+                 "decode_launches_per_step": launches, "graph_replays": engine.runner.graph_replays,
+                 "weight_bytes_per_step": engine.model.weight_bytes()}
+            if not args.skip_points:
+                r["kernels"] = kernel_table(engine, names, PREFILL_TOKENS, args.batch, ctx, 0, pk, extra={"ctx": ctx})
+            ops.check_kernel_status()
+            res[which] = r
+            del engine
+            torch.cuda.empty_cache()
+        out["sizes"][key] = res
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 # Kinds of launches that `--without` leaves out of a decode step, to see what each costs inside it.
 LEFT_OUT = ("norms", "rotation", "attention", "qkv", "o", "gate_up", "down", "head", "products")
 
@@ -644,10 +754,11 @@ def main() -> int:
     ap.add_argument("--without", default=None, choices=sorted(LEFT_OUT),
                     help="with --only decode: time the step with the launches of one kind left out (its results are "
                          "wrong; the difference to the full step is what that kind costs inside the step)")
-    ap.add_argument("--workload", default="headline", choices=["headline", "serving", "longctx", "notirax"],
-                    help="serving: 64 requests on the 3B shape; longctx: 8 x 16,384 tokens on the 8B shape; notirax: "
-                         "prefill and decode of the Notirax design beside the Llama decoder at equal size, per kernel")
-    ap.add_argument("--size", default=None, choices=sorted(NOTIRAX_SIZES), help="with --workload notirax: one size only")
+    ap.add_argument("--workload", default="headline", choices=["headline", "serving", "longctx", "notirax", "luzinex"],
+                    help="serving: 64 requests on the 3B shape; longctx: 8 x 16,384 tokens on the 8B shape; notirax / "
+                         "luzinex: prefill and decode of that design beside the Llama decoder at equal size, per kernel")
+    ap.add_argument("--size", default=None, choices=sorted(set(NOTIRAX_SIZES) | set(LUZINEX_SIZES)),
+                    help="with --workload notirax or luzinex: one size only")
     args = ap.parse_args()
     args.shape_given = args.shape is not None
     args.shape = args.shape or "1b"
@@ -661,6 +772,8 @@ def main() -> int:
     args.warmup = max(args.warmup, 3)
     if args.workload == "notirax":
         return run_notirax(args)
+    if args.workload == "luzinex":
+        return run_luzinex(args)
     if args.workload != "headline":
         return run_workload(args)
 

@@ -97,6 +97,9 @@ _SIGNATURES = {
     "mf_latent_query": [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P],
     "mf_head_linear": [_P, c_longlong, c_int, _P, _P, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, _P,
                        c_longlong, _P],
+    "mf_head_linear_mma_ok": [c_longlong, c_int, c_int],
+    "mf_head_linear_mma": [_P, c_longlong, c_int, _P, _P, c_longlong, c_int, c_int, c_int, c_int, c_int, _P,
+                           c_longlong, _P],
     "mf_retention_prepare": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P, _P, _P],
     "mf_retention_recurrence": [_P, _P, c_int, c_longlong, _P, _P, c_longlong, _P, _P, _P, _P, c_int, c_int, c_int,
                                 c_int, _P],

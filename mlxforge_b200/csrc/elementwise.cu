@@ -433,6 +433,82 @@ __global__ void add_rmsnorm_pair_kernel(float* __restrict__ resid, const TD* __r
   }
 }
 
+// The serving case in 16-byte pieces: bfloat16 deltas and outputs, H a multiple of 8 and at most
+// 8 * 256 * NV, every value held in registers between the two passes.
+template <int NV>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_pair_bf16_vec_kernel(float* __restrict__ resid, const __nv_bfloat16* __restrict__ d1,
+                                 const __nv_bfloat16* __restrict__ d2, const float* __restrict__ w1,
+                                 const float* __restrict__ w2, float eps, __nv_bfloat16* __restrict__ out1,
+                                 __nv_bfloat16* __restrict__ out2, const int* __restrict__ rows, int H) {
+  __shared__ float red[32];
+  pdl_launch();              // the products after this one fetch their weights meanwhile
+  pdl_wait();
+  const int r = blockIdx.x;
+  const long long src = rows ? rows[r] : r;
+  float* x = resid + src * H;
+  const __nv_bfloat16* a = d1 ? d1 + src * H : nullptr;
+  const __nv_bfloat16* b = d2 ? d2 + src * H : nullptr;
+  float v[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV; j++) {
+    const int i = (j * 256 + threadIdx.x) * 8;
+    if (i < H) {
+      const float4 xa = *reinterpret_cast<const float4*>(x + i), xb = *reinterpret_cast<const float4*>(x + i + 4);
+      v[j][0] = xa.x; v[j][1] = xa.y; v[j][2] = xa.z; v[j][3] = xa.w;
+      v[j][4] = xb.x; v[j][5] = xb.y; v[j][6] = xb.z; v[j][7] = xb.w;
+      if (a || b) {
+        float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int which = 0; which < 2; which++) {
+          const __nv_bfloat16* dp = which ? b : a;
+          if (!dp) continue;
+          const uint4 dv = *reinterpret_cast<const uint4*>(dp + i);
+          const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&dv);
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const float2 f = __bfloat1622float2(p[e]);
+            d[2 * e] += f.x;
+            d[2 * e + 1] += f.y;
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[j][e] += d[e];
+        if (!rows) {
+          *reinterpret_cast<float4*>(x + i) = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
+          *reinterpret_cast<float4*>(x + i + 4) = make_float4(v[j][4], v[j][5], v[j][6], v[j][7]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; e++) ss += v[j][e] * v[j][e];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int which = 0; which < 2; which++) {
+    __nv_bfloat16* o = which ? out2 : out1;
+    const float* w = which ? w2 : w1;
+    if (!o) continue;
+    o += (long long)r * H;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+      const int i = (j * 256 + threadIdx.x) * 8;
+      if (i < H) {
+        const float4 wa = *reinterpret_cast<const float4*>(w + i), wb = *reinterpret_cast<const float4*>(w + i + 4);
+        uint4 pk;
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&pk);
+        p[0] = __floats2bfloat162_rn(v[j][0] * inv * wa.x, v[j][1] * inv * wa.y);
+        p[1] = __floats2bfloat162_rn(v[j][2] * inv * wa.z, v[j][3] * inv * wa.w);
+        p[2] = __floats2bfloat162_rn(v[j][4] * inv * wb.x, v[j][5] * inv * wb.y);
+        p[3] = __floats2bfloat162_rn(v[j][6] * inv * wb.z, v[j][7] * inv * wb.w);
+        *reinterpret_cast<uint4*>(o + i) = pk;
+      }
+    }
+  }
+}
+
 MF_API int mf_add_rmsnorm_pair(float* resid, const void* d1, const void* d2, int delta_dtype, const float* w1,
                                const float* w2, float eps, void* out1, void* out2, int out_dtype, const int* rows,
                                int n_rows, int H, cudaStream_t stream) {
@@ -440,6 +516,20 @@ MF_API int mf_add_rmsnorm_pair(float* resid, const void* d1, const void* d2, int
   if (out2 && !w2) return MF_ERR_BAD_ARG;
   const int threads = H >= 1024 ? 256 : 128;
   mf_count(MF_K_NORM_PAIR);
+  if (out_dtype == MF_BF16 && ((!d1 && !d2) || delta_dtype == MF_BF16) && H % 8 == 0 && H <= 8 * 256 * 4 &&
+      (((uintptr_t)resid | (uintptr_t)d1 | (uintptr_t)d2 | (uintptr_t)w1 | (uintptr_t)w2 | (uintptr_t)out1 |
+        (uintptr_t)out2) & 15) == 0) {
+    const __nv_bfloat16 *a = (const __nv_bfloat16*)d1, *b = (const __nv_bfloat16*)d2;
+    __nv_bfloat16 *o1 = (__nv_bfloat16*)out1, *o2 = (__nv_bfloat16*)out2;
+    if (H <= 2048)
+      return (int)launch_dep(add_rmsnorm_pair_bf16_vec_kernel<1>, dim3(n_rows), dim3(256), 0, stream, resid, a, b, w1, w2,
+                             eps, o1, o2, rows, H);
+    if (H <= 4096)
+      return (int)launch_dep(add_rmsnorm_pair_bf16_vec_kernel<2>, dim3(n_rows), dim3(256), 0, stream, resid, a, b, w1, w2,
+                             eps, o1, o2, rows, H);
+    return (int)launch_dep(add_rmsnorm_pair_bf16_vec_kernel<4>, dim3(n_rows), dim3(256), 0, stream, resid, a, b, w1, w2,
+                           eps, o1, o2, rows, H);
+  }
 #define LAUNCH(TD, TO)                                                                                        \
   return (int)launch_dep(add_rmsnorm_pair_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, stream, resid,      \
                          (const TD*)d1, (const TD*)d2, w1, w2, eps, (TO*)out1, (TO*)out2, rows, H)

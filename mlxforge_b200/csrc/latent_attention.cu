@@ -146,6 +146,120 @@ head_linear_kernel(const T* __restrict__ x, long long x_ld, int x_hs, const T* _
   }
 }
 
+// ---------------------------------------------------------------------------- the same on tensor cores
+// bfloat16, many tokens: a block per (64 tokens, head, 64 outputs).  The head's rows of x and of W
+// (both K wide, K a multiple of 16) are staged whole in shared memory, each of the four warps owns
+// 16 tokens and all 64 outputs: mma.sync m16n8k16 over K, 32-bit accumulators, the gate in the
+// epilogue.  The order of a sum depends on K alone, so a token's result does not depend on the batch.
+namespace {
+constexpr int HM_BM = 64, HM_BN = 64, HM_WARPS = 4;
+
+__device__ __forceinline__ void hm_cp_async_16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void hm_ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void hm_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+}  // namespace
+
+__global__ void __launch_bounds__(HM_WARPS * 32)
+head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int x_hs, const __nv_bfloat16* __restrict__ w,
+                       __nv_bfloat16* __restrict__ out, long long out_ld, int out_hs, int T, int N, int K,
+                       const __nv_bfloat16* __restrict__ gate, long long gate_ld) {
+  extern __shared__ __align__(16) unsigned char hm_smem[];
+  const int ld = K + 8, chunks = K >> 3;
+  __nv_bfloat16* x_s = reinterpret_cast<__nv_bfloat16*>(hm_smem);      // [HM_BM][ld]
+  __nv_bfloat16* w_s = x_s + HM_BM * ld;                                // [HM_BN][ld]
+  const int t0 = blockIdx.x * HM_BM, h = blockIdx.y, n0 = blockIdx.z * HM_BN;
+  const __nv_bfloat16* wh = w + ((long long)h * N + n0) * K;
+  for (int i = threadIdx.x; i < HM_BN * chunks; i += HM_WARPS * 32) {      // the weights never change: before the wait
+    const int r = i / chunks, c = i - r * chunks;
+    hm_cp_async_16(w_s + r * ld + c * 8, wh + (long long)min(r, N - n0 - 1) * K + c * 8, n0 + r < N);
+  }
+  pdl_launch();
+  pdl_wait();
+  for (int i = threadIdx.x; i < HM_BM * chunks; i += HM_WARPS * 32) {
+    const int r = i / chunks, c = i - r * chunks;
+    const int t = min(t0 + r, T - 1);
+    hm_cp_async_16(x_s + r * ld + c * 8, x + t * x_ld + (long long)h * x_hs + c * 8, t0 + r < T);
+  }
+  asm volatile("cp.async.commit_group;\n" ::: "memory");
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  float acc[HM_BN / 8][4];
+#pragma unroll
+  for (int j = 0; j < HM_BN / 8; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  for (int kk = 0; kk < K; kk += 16) {
+    unsigned a[4];
+    hm_ldmatrix_x4(a, x_s + (warp * 16 + (lane & 15)) * ld + kk + (lane >> 4) * 8);
+#pragma unroll
+    for (int j = 0; j < HM_BN / 8; j += 2) {
+      unsigned b[4];
+      const int mi = lane >> 3, r = lane & 7;
+      hm_ldmatrix_x4(b, w_s + (j * 8 + (mi >> 1) * 8 + r) * ld + kk + (mi & 1) * 8);
+      hm_mma(acc[j], a, b[0], b[1]);
+      hm_mma(acc[j + 1], a, b[2], b[3]);
+    }
+  }
+#pragma unroll
+  for (int hh = 0; hh < 2; hh++) {
+    const int t = t0 + warp * 16 + g + hh * 8;
+    if (t >= T) continue;
+    __nv_bfloat16* orow = out + t * out_ld + (long long)h * out_hs;
+    const __nv_bfloat16* grow = gate ? gate + t * gate_ld + (long long)h * N : nullptr;
+#pragma unroll
+    for (int j = 0; j < HM_BN / 8; j++) {
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const int n = n0 + j * 8 + tq * 2 + e;
+        if (n < N) {
+          float v = acc[j][hh * 2 + e];
+          if (grow) v *= 1.0f / (1.0f + __expf(-__bfloat162float(grow[n])));
+          orow[n] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+  }
+}
+
+// Whether the tensor-core kernel takes these operands: K a multiple of 16 that fits shared memory,
+// rows and heads of x starting on 16-byte boundaries.
+MF_API int mf_head_linear_mma_ok(long long x_ld, int x_hs, int K) {
+  return (K % 16 == 0 && K <= 512 && x_ld % 8 == 0 && x_hs % 8 == 0) ? 1 : 0;
+}
+
+MF_API int mf_head_linear_mma(const void* x, long long x_ld, int x_hs, const void* w, void* out, long long out_ld,
+                              int out_hs, int T, int n_heads, int N, int K, const void* gate, long long gate_ld,
+                              cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (!mf_head_linear_mma_ok(x_ld, x_hs, K) || n_heads <= 0 || n_heads > 65535 || N <= 0) return MF_ERR_BAD_ARG;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return MF_ERR_BAD_ARG;
+  const size_t smem = (size_t)(HM_BM + HM_BN) * (K + 8) * sizeof(__nv_bfloat16);
+  static DeviceOnce once;
+  const int dev = mf_current_device();
+  if (dev < 0) return MF_ERR_BAD_ARG;
+  if (!once.done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(head_linear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    once.done[dev] = true;
+  }
+  mf_count(MF_K_HEAD_LINEAR_MMA);
+  dim3 grid((T + HM_BM - 1) / HM_BM, n_heads, (N + HM_BN - 1) / HM_BN);
+  return (int)launch_dep(head_linear_mma_kernel, grid, dim3(HM_WARPS * 32), smem, stream, (const __nv_bfloat16*)x, x_ld,
+                         x_hs, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_ld, out_hs, T, N, K,
+                         (const __nv_bfloat16*)gate, gate_ld);
+}
+
 MF_API int mf_head_linear(const void* x, long long x_ld, int x_hs, const void* w, void* out, long long out_ld,
                           int out_hs, int dtype, int T, int n_heads, int N, int K, const void* gate,
                           long long gate_ld, cudaStream_t stream) {

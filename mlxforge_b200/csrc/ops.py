@@ -229,6 +229,21 @@ def head_linear(x: torch.Tensor, x_ld: int, x_hs: int, w: torch.Tensor, out: tor
                                    dtype_code(w), T, H, N, K, _ptr(gate), gate_ld, _stream()), "head_linear")
 
 
+def head_linear_mma_ok(x: torch.Tensor, x_ld: int, x_hs: int, w: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel of ``head_linear`` takes these operands."""
+    return (w.dtype == torch.bfloat16 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and bool(library().mf_head_linear_mma_ok(x_ld, x_hs, w.shape[2])))
+
+
+def head_linear_mma(x: torch.Tensor, x_ld: int, x_hs: int, w: torch.Tensor, out: torch.Tensor, out_ld: int, out_hs: int,
+                    T: int, gate: Optional[torch.Tensor] = None, gate_ld: int = 0) -> None:
+    """``head_linear`` for many bfloat16 tokens, on the tensor cores (mma.sync tiles of 64 tokens x 64 outputs)."""
+    _need_cuda(w)
+    H, N, K = w.shape
+    check(library().mf_head_linear_mma(x.data_ptr(), x_ld, x_hs, w.data_ptr(), out.data_ptr(), out_ld, out_hs, T, H, N,
+                                       K, _ptr(gate), gate_ld, _stream()), "head_linear_mma")
+
+
 def retention_prepare(proj: torch.Tensor, n_heads: int, dim: int, rot: int, k_scale: float, positions: torch.Tensor,
                       inv_f, inv_d, qk: torch.Tensor) -> None:
     """Rows [queries | keys | ...] -> 32-bit [T, 2 heads dim]: both rotated, keys times ``k_scale``."""

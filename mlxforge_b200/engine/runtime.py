@@ -114,8 +114,12 @@ class Runtime:
                     gate_ld: int = 0):
         """A product per head: ``out[t, h, :] = w[h] @ x[t, h, :]`` for ``w`` [heads, N, K], rows and heads of
         ``x`` and ``out`` at the given strides (in elements), optionally times ``sigmoid(gate[t, h * N + n])``;
-        32-bit accumulation, one rounding."""
-        ops.head_linear(x, x_ld, x_hs, w, out, out_ld, out_hs, T, gate, gate_ld)
+        32-bit accumulation, one rounding.  More than 16 bfloat16 tokens take the tensor-core kernel where the
+        sizes allow it; few tokens and the 32-bit path the kernel with a warp per output."""
+        if T > self.stream_max_rows and ops.head_linear_mma_ok(x, x_ld, x_hs, w):
+            ops.head_linear_mma(x, x_ld, x_hs, w, out, out_ld, out_hs, T, gate, gate_ld)
+        else:
+            ops.head_linear(x, x_ld, x_hs, w, out, out_ld, out_hs, T, gate, gate_ld)
         return out
 
     def _skinny(self, x, w) -> bool:

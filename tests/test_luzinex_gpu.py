@@ -88,6 +88,39 @@ def test_gelu_gated_feed_forward(dtype, H, ff, T):
     assert np.max(np.abs(got - want)) < tol(dtype, np.abs(want).max())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,heads,N,K,gated", [(5, 3, 7, 12, True), (1, 1, 40, 16, False), (150, 4, 48, 32, True),
+                                               (70, 2, 100, 64, True), (300, 6, 64, 48, False), (33, 2, 24, 20, True)])
+def test_a_product_per_head(dtype, T, heads, N, K, gated):
+    """Rows and heads of x and of the result sit inside wider rows (other columns must stay as they are); few
+    tokens and sizes the tensor-core kernel does not take go through the kernel with a warp per output."""
+    import torch
+    from mlxforge_b200.csrc import binding
+    from mlxforge_b200.engine.runtime import Runtime
+    rng = np.random.default_rng(T + N)
+    rt = Runtime(tdt(dtype))
+    x_hs, out_hs = K + 8, N + 3
+    x_ld, out_ld = heads * x_hs + 16, heads * out_hs + 5
+    x = rand(rng, T, x_ld)
+    w = rand(rng, heads, N, K, std=K ** -0.5)
+    gate = rand(rng, T, heads * N + 6)
+    out = torch.full((T, out_ld), 7.0, dtype=tdt(dtype), device="cuda")
+    xd, gd = dev(x, tdt(dtype)), dev(gate, tdt(dtype))
+    before = binding.kernel_launches()
+    rt.head_linear(xd[:, 8:], x_ld, x_hs, dev(w, tdt(dtype)), out[:, 2:], out_ld, out_hs, T,
+                   gd[:, 6:] if gated else None, gate.shape[1])
+    ran = {k: v - before[k] for k, v in binding.kernel_launches().items() if v - before[k]}
+    want = np.full((T, out_ld), 7.0)
+    for h in range(heads):
+        y = x[:, 8 + h * x_hs:8 + h * x_hs + K].astype(np.float64) @ w[h].astype(np.float64).T
+        if gated:
+            y = y * P.sigmoid(gate[:, 6 + h * N:6 + (h + 1) * N].astype(np.float64))
+        want[:, 2 + h * out_hs:2 + h * out_hs + N] = y
+    assert np.max(np.abs(host(out) - want)) < tol(dtype, 4.0)
+    tensor_cores = dtype == "bfloat16" and T > 16 and K % 16 == 0
+    assert ("head_linear_mma" in ran) == tensor_cores and ("head_linear" in ran) != tensor_cores, ran
+
+
 # ----------------------------------------------------------------------------- the attention whose values are its keys
 
 SINK_CASES = {
@@ -461,7 +494,7 @@ def test_serving_shapes_take_the_fast_kernels(models, tmp_path):
     """Configuration C in bfloat16: which kernels its prompts and its decoding go through."""
     reqs = models[("C", False)][2]
     ran = _check(models, "C", False, "bfloat16", TT.decode_tail(reqs, tail=8), tmp_path)
-    for k in ("norm_pair", "rope_store", "latent_prepare", "latent_query", "head_linear", "retention_prepare",
+    for k in ("norm_pair", "rope_store", "latent_prepare", "latent_query", "head_linear", "head_linear_mma", "retention_prepare",
               "retention_recurrence", "retention_output", "attn_prefill_mma", "attn_decode", "attn_decode_merge"):
         assert ran.get(k, 0) > 0, (k, ran)
     assert "attn_generic" not in ran, ran
