@@ -497,13 +497,14 @@ def kernel_work(name, a, k, info):
             return (0, 2.0 * seen * H * (hd + vd), 0)
         seen = info["seqs"] * (min(info["ctx"], window + keep) if window else info["ctx"])
         return (seen * n_kv * (hd + (0 if in_k else vd)) * 2, 0, 0)
-    if name == "head_linear":
+    if name in ("head_linear", "head_linear_mma"):
         w, n_tok = a[3], a[7]
         heads, n, kk = w.shape
         return (_nbytes(w) + n_tok * heads * (n + kk) * w.element_size(), 2.0 * n_tok * heads * n * kk, 0)
     if name == "retention_recurrence":
         qk, state, o, nh, dim, vdim = a[0], a[4], a[6], a[7], a[8], a[9]
-        return (_nbytes(qk, o) + T * nh * vdim * 2 + 2 * info["seqs"] * nh * dim * vdim * 4, 0, 4.0 * T * nh * dim * vdim)
+        return (_nbytes(qk) + 4 * T * nh * vdim + T * nh * vdim * 2 + 2 * info["seqs"] * nh * dim * vdim * 4, 0,
+                4.0 * T * nh * dim * vdim)
     if name in ("rope_store", "latent_prepare", "latent_query", "retention_prepare", "retention_output"):
         return (_nbytes(*[t for t in a if hasattr(t, "numel") and t.dim() >= 2 and t.numel() < (1 << 28)]), 0, 0)
     if name in ("gemm_bf16", "stream_linear"):
@@ -627,7 +628,7 @@ LUZINEX_SIZES = {
               l_heads=16, l_dim=64, l_rot=32, l_vdim=64, q_rank=768, kv_rank=192, r_heads=16, r_dim=128, r_vdim=128,
               context=4096),
 }
-LUZINEX_KERNELS = ("embed", "add_rmsnorm_pair", "rope_store", "latent_prepare", "latent_query", "head_linear",
+LUZINEX_KERNELS = ("embed", "add_rmsnorm_pair", "rope_store", "latent_prepare", "latent_query", "head_linear", "head_linear_mma",
                    "attention_prefill_ex", "attention_decode_ex", "attention_generic_ex", "retention_prepare",
                    "retention_recurrence", "retention_chunked", "retention_output", "swiglu", "stream_linear", "gemm_bf16")
 

@@ -101,9 +101,10 @@ _SIGNATURES = {
     "mf_head_linear_mma": [_P, c_longlong, c_int, _P, _P, c_longlong, c_int, c_int, c_int, c_int, c_int, _P,
                            c_longlong, _P],
     "mf_retention_prepare": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P, _P, _P],
-    "mf_retention_recurrence": [_P, _P, c_int, c_longlong, _P, _P, c_longlong, _P, _P, _P, _P, c_int, c_int, c_int,
-                                c_int, _P],
-    "mf_retention_output": [_P, _P, c_int, c_longlong, c_float, _P, c_int, c_int, c_int, _P],
+    "mf_retention_parts": [c_int, c_int, c_int, c_longlong],
+    "mf_retention_recurrence": [_P, _P, c_int, c_longlong, _P, _P, c_longlong, _P, _P, _P, _P, c_longlong, c_int, c_int,
+                                c_int, c_int, _P],
+    "mf_retention_output": [_P, c_int, c_longlong, _P, c_int, c_longlong, c_float, _P, c_int, c_int, c_int, _P],
 }
 
 MF_ERRORS = {10001: "a size or option this kernel does not take", 10002: "an unsupported dtype"}

@@ -253,22 +253,33 @@ def retention_prepare(proj: torch.Tensor, n_heads: int, dim: int, rot: int, k_sc
                                          _stream()), "retention_prepare")
 
 
+def retention_parts(dim: int, vdim: int, v: torch.Tensor, v_ld: int) -> int:
+    """How many partial read-outs ``retention_recurrence`` writes for these sizes (it spreads a head's state over
+    that many groups of rows where the sizes come in whole pieces); ``retention_output`` sums them."""
+    return int(library().mf_retention_parts(dim, vdim, dtype_code(v), v_ld))
+
+
 def retention_recurrence(qk: torch.Tensor, v: torch.Tensor, v_ld: int, decay: torch.Tensor, state: torch.Tensor,
                          batch, o_out: torch.Tensor, n_heads: int, dim: int, vdim: int) -> None:
-    """``v`` points at the first value of the first token (rows ``v_ld`` elements apart)."""
+    """``v`` points at the first value of the first token (rows ``v_ld`` elements apart).  ``o_out``
+    [``retention_parts``, T, n_heads * vdim] receives the partial read-outs."""
     _need_cuda(qk, decay, state, o_out)
+    if o_out.dim() != 3 or o_out.shape[0] != retention_parts(dim, vdim, v, v_ld):
+        raise KernelError("retention_recurrence: o_out must hold retention_parts(...) partial read-outs")
     check(library().mf_retention_recurrence(qk.data_ptr(), v.data_ptr(), dtype_code(v), v_ld, decay.data_ptr(),
                                             state.data_ptr(), state.stride(0), batch.seq_q_start.data_ptr(),
                                             batch.seq_q_len.data_ptr(), batch.slots.data_ptr(), o_out.data_ptr(),
-                                            batch.n_seqs, n_heads, dim, vdim, _stream()), "retention_recurrence")
+                                            o_out.stride(0), batch.n_seqs, n_heads, dim, vdim, _stream()),
+          "retention_recurrence")
 
 
 def retention_output(o: torch.Tensor, gate: torch.Tensor, gate_ld: int, eps: float, out: torch.Tensor, n_heads: int,
                      vdim: int) -> None:
-    """``gate`` points at the first gate of the first token; rows are ``gate_ld`` elements apart."""
+    """``o`` [parts, T, n_heads * vdim]: the partial read-outs, summed here.  ``gate`` points at the first gate of
+    the first token; rows are ``gate_ld`` elements apart."""
     _need_cuda(o, out)
-    check(library().mf_retention_output(o.data_ptr(), gate.data_ptr(), dtype_code(out), gate_ld, eps, out.data_ptr(),
-                                        o.shape[0], n_heads, vdim, _stream()), "retention_output")
+    check(library().mf_retention_output(o.data_ptr(), o.shape[0], o.stride(0), gate.data_ptr(), dtype_code(out), gate_ld,
+                                        eps, out.data_ptr(), o.shape[1], n_heads, vdim, _stream()), "retention_output")
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

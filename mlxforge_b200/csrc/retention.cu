@@ -13,7 +13,8 @@
 //    dim/8 of its rows in registers; q and k of the coming tokens are staged in shared memory,
 //    eight tokens at a time.  A step continues from the slot's state, so the result does not
 //    depend on how a prompt was cut.
-//  * retention_output: per token and head the read-out over its root mean square, times silu(gate).
+//  * retention_output: per token and head the read-out (summed over the row groups that a staged
+//    launch spreads a head's state over) over its root mean square, times silu(gate).
 #include "rotary.cuh"
 
 namespace {
@@ -136,12 +137,128 @@ retention_recurrence_kernel(const float* __restrict__ qk, const T* __restrict__ 
   }
 }
 
+// ---------------------------------------------------------------------------- the same, staged
+// For sizes in whole pieces (dim a multiple of 32, vdim of 16, 16-byte aligned rows): a block owns
+// RS_ROWS rows x RT_COLS columns of S, so that a head's state is spread over dim/RS_ROWS x vdim/RT_COLS
+// blocks (an element of S depends on no other element; only the read-out sums over rows, and that sum
+// is finished by the output kernel over the row groups' partial read-outs).  The block's share of q, k
+// and v of the coming tokens arrives through a ring of cp.async stages, RS_CHUNK tokens each, so that no
+// token waits for memory.
+namespace {
+constexpr int RS_ROWS = 32;
+constexpr int RS_RPL = RS_ROWS / RT_LANES;
+constexpr int RS_CHUNK = 16;
+constexpr int RS_STAGES = 4;
+
+__device__ __forceinline__ void rs_cp_async_16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+}  // namespace
+
+template <typename T>
+__global__ void __launch_bounds__(RT_THREADS)
+retention_recurrence_staged_kernel(const float* __restrict__ qk, const T* __restrict__ v, long long v_ld,
+                                   const float* __restrict__ decay, float* __restrict__ state, long long state_stride,
+                                   const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
+                                   const int* __restrict__ slots, float* __restrict__ o_part, long long part_stride,
+                                   int n_heads, int dim, int vdim) {
+  constexpr int V_PIECES = RT_COLS * sizeof(T) / 16;               // 16-byte pieces of a token's values
+  constexpr int PIECES = 2 * RS_ROWS / 4 + V_PIECES;               // q, k, v of one token
+  constexpr int TOKEN_FLOATS = 2 * RS_ROWS + RT_COLS * sizeof(T) / 4;
+  __shared__ __align__(16) float ring[RS_STAGES][RS_CHUNK][TOKEN_FLOATS];
+  pdl_launch();
+  pdl_wait();
+  const int s = blockIdx.x, h = blockIdx.y;
+  const int n_cb = vdim / RT_COLS;
+  const int rg = blockIdx.z / n_cb, c0 = (blockIdx.z - rg * n_cb) * RT_COLS, r0 = rg * RS_ROWS;
+  const int lane = threadIdx.x % RT_LANES, cl = threadIdx.x / RT_LANES;
+  const int t0 = seq_q_start[s], n = seq_q_len[s];
+  const float g = decay[h];
+  float* S = state + (long long)slots[s] * state_stride + ((long long)h * dim + r0) * vdim + c0 + cl;
+  float st[RS_RPL];
+#pragma unroll
+  for (int i = 0; i < RS_RPL; i++) st[i] = S[(long long)(lane + i * RT_LANES) * vdim];
+  const int n_chunks = (n + RS_CHUNK - 1) / RS_CHUNK;
+
+  auto fetch = [&](int chunk) {
+    const int stage = chunk % RS_STAGES;
+    const int nb = min(RS_CHUNK, n - chunk * RS_CHUNK);
+    for (int i = threadIdx.x; i < nb * PIECES; i += RT_THREADS) {
+      const int tt = i / PIECES, p = i - tt * PIECES;
+      const long long t = t0 + chunk * RS_CHUNK + tt;
+      float* dst = &ring[stage][tt][0] + p * 4;
+      if (p < 2 * RS_ROWS / 4) {
+        const int which = p / (RS_ROWS / 4), q4 = p - which * (RS_ROWS / 4);      // 0: q, 1: k
+        rs_cp_async_16(dst, qk + t * 2 * n_heads * dim + (long long)(which * n_heads + h) * dim + r0 + q4 * 4);
+      } else {
+        const int v4 = p - 2 * RS_ROWS / 4;
+        rs_cp_async_16(dst, reinterpret_cast<const char*>(v + t * v_ld + (long long)h * vdim + c0) + v4 * 16);
+      }
+    }
+  };
+#pragma unroll
+  for (int c = 0; c < RS_STAGES - 1; c++) {
+    if (c < n_chunks) fetch(c);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  }
+  float* o = o_part + (long long)rg * part_stride + (long long)h * vdim + c0 + cl;
+  for (int chunk = 0; chunk < n_chunks; chunk++) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(RS_STAGES - 2) : "memory");
+    __syncthreads();          // the chunk has landed for everyone, and everyone is done with the stage refilled next
+    if (chunk + RS_STAGES - 1 < n_chunks) fetch(chunk + RS_STAGES - 1);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    const int stage = chunk % RS_STAGES;
+    const int nb = min(RS_CHUNK, n - chunk * RS_CHUNK);
+    for (int tt = 0; tt < nb; tt++) {
+      const float* qs = &ring[stage][tt][0];
+      const float* ks = qs + RS_ROWS;
+      const float vc = to_f32<T>(reinterpret_cast<const T*>(ks + RS_ROWS)[cl]);
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < RS_RPL; i++) {
+        const int r = lane + i * RT_LANES;
+        st[i] = fmaf(g, st[i], ks[r] * vc);
+        acc = fmaf(st[i], qs[r], acc);
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (lane == 0) o[(long long)(t0 + chunk * RS_CHUNK + tt) * n_heads * vdim] = acc;
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < RS_RPL; i++) S[(long long)(lane + i * RT_LANES) * vdim] = st[i];
+}
+
+// How many partial read-outs (row groups) a launch writes: retention_output sums them.
+MF_API int mf_retention_parts(int dim, int vdim, int v_dtype, long long v_ld) {
+  const int vb = v_dtype == MF_F32 ? 4 : 2;
+  const bool staged = dim % RS_ROWS == 0 && vdim % RT_COLS == 0 && (v_ld * vb) % 16 == 0 && (vdim * vb) % 16 == 0;
+  return staged ? dim / RS_ROWS : 1;
+}
+
 MF_API int mf_retention_recurrence(const float* qk, const void* v, int v_dtype, long long v_ld, const float* decay,
                                    float* state, long long state_stride, const int* seq_q_start,
-                                   const int* seq_q_len, const int* slots, float* o_out, int n_seqs, int n_heads,
-                                   int dim, int vdim, cudaStream_t stream) {
+                                   const int* seq_q_len, const int* slots, float* o_out, long long part_stride,
+                                   int n_seqs, int n_heads, int dim, int vdim, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (dim <= 0 || dim > 32 * RT_LANES || vdim <= 0 || n_heads <= 0 || n_heads > 65535) return MF_ERR_BAD_ARG;
+  // o_out holds mf_retention_parts(...) partial read-outs, `part_stride` floats apart
+  if (mf_retention_parts(dim, vdim, v_dtype, v_ld) > 1 && ((uintptr_t)qk & 15) == 0 && ((uintptr_t)v & 15) == 0 &&
+      (v_dtype == MF_F32 || v_dtype == MF_BF16)) {
+    dim3 sgrid(n_seqs, n_heads, (dim / RS_ROWS) * (vdim / RT_COLS));
+    mf_count(MF_K_RETENTION_RECURRENCE);
+    if (v_dtype == MF_F32)
+      return (int)launch_dep(retention_recurrence_staged_kernel<float>, sgrid, dim3(RT_THREADS), 0, stream, qk,
+                             (const float*)v, v_ld, decay, state, state_stride, seq_q_start, seq_q_len, slots, o_out,
+                             part_stride, n_heads, dim, vdim);
+    return (int)launch_dep(retention_recurrence_staged_kernel<__nv_bfloat16>, sgrid, dim3(RT_THREADS), 0, stream, qk,
+                           (const __nv_bfloat16*)v, v_ld, decay, state, state_stride, seq_q_start, seq_q_len, slots,
+                           o_out, part_stride, n_heads, dim, vdim);
+  }
+  if (mf_retention_parts(dim, vdim, v_dtype, v_ld) > 1) return MF_ERR_BAD_ARG;     // the caller sized o_out for parts
   dim3 grid(n_seqs, n_heads, (vdim + RT_COLS - 1) / RT_COLS);
   const size_t smem = (size_t)RT_CHUNK * (2 * dim + RT_COLS) * sizeof(float);
   const int per = (dim + RT_LANES - 1) / RT_LANES;
@@ -164,8 +281,9 @@ MF_API int mf_retention_recurrence(const float* qk, const void* v, int v_dtype, 
 
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]); a warp per (token, head)
 template <typename T>
-__global__ void retention_output_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long gate_ld,
-                                        float eps, T* __restrict__ out, int n_heads, int vdim) {
+__global__ void retention_output_kernel(const float* __restrict__ o, int n_parts, long long part_stride,
+                                        const T* __restrict__ gate, long long gate_ld, float eps, T* __restrict__ out,
+                                        int n_heads, int vdim) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.x;
@@ -173,28 +291,39 @@ __global__ void retention_output_kernel(const float* __restrict__ o, const T* __
   for (int h = warp; h < n_heads; h += nw) {
     const float* orow = o + ((long long)t * n_heads + h) * vdim;
     const T* grow = gate + (long long)t * gate_ld + (long long)h * vdim;
+    // the read-out is the sum of the row groups' partial read-outs, added in their order
+    auto read = [&](int d) {
+      float v = orow[d];
+      for (int p = 1; p < n_parts; p++) v += orow[p * part_stride + d];
+      return v;
+    };
     float ss = 0.f;
-    for (int d = lane; d < vdim; d += 32) ss += orow[d] * orow[d];
+    for (int d = lane; d < vdim; d += 32) {
+      const float v = read(d);
+      ss += v * v;
+    }
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
     T* dst = out + ((long long)t * n_heads + h) * vdim;
     for (int d = lane; d < vdim; d += 32) {
       const float g = to_f32<T>(grow[d]);
-      dst[d] = from_f32<T>(orow[d] * inv * (g / (1.0f + expf(-g))));
+      dst[d] = from_f32<T>(read(d) * inv * (g / (1.0f + expf(-g))));
     }
   }
 }
 
-MF_API int mf_retention_output(const float* o, const void* gate, int dtype, long long gate_ld, float eps, void* out,
-                               int T, int n_heads, int vdim, cudaStream_t stream) {
+MF_API int mf_retention_output(const float* o, int n_parts, long long part_stride, const void* gate, int dtype,
+                               long long gate_ld, float eps, void* out, int T, int n_heads, int vdim,
+                               cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (n_parts < 1) return MF_ERR_BAD_ARG;
   mf_count(MF_K_RETENTION_OUTPUT);
   const int threads = n_heads >= 8 ? 256 : 32 * (n_heads > 0 ? n_heads : 1);
   if (dtype == MF_F32)
-    return (int)launch_dep(retention_output_kernel<float>, dim3(T), dim3(threads), 0, stream, o, (const float*)gate,
-                           gate_ld, eps, (float*)out, n_heads, vdim);
+    return (int)launch_dep(retention_output_kernel<float>, dim3(T), dim3(threads), 0, stream, o, n_parts, part_stride,
+                           (const float*)gate, gate_ld, eps, (float*)out, n_heads, vdim);
   if (dtype == MF_BF16)
-    return (int)launch_dep(retention_output_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, o,
-                           (const __nv_bfloat16*)gate, gate_ld, eps, (__nv_bfloat16*)out, n_heads, vdim);
+    return (int)launch_dep(retention_output_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, o, n_parts,
+                           part_stride, (const __nv_bfloat16*)gate, gate_ld, eps, (__nv_bfloat16*)out, n_heads, vdim);
   return MF_ERR_BAD_DTYPE;
 }

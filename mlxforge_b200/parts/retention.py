@@ -82,8 +82,9 @@ class Retention(Mixer):
         ld = proj.shape[1]
         qk = rt.buffer("ret.qk", (T, 2 * nh * d), f32)
         ops.retention_prepare(proj, nh, d, self.rot, self.k_scale, batch.positions, self.inv_f, self.inv_d, qk)
-        o = rt.buffer("ret.o", (T, nh * dv), f32)
-        ops.retention_recurrence(qk, proj[:, 2 * nh * d:], ld, self.decay, cache.tensor, batch, o, nh, d, dv)
+        v = proj[:, 2 * nh * d:]
+        o = rt.buffer("ret.o", (ops.retention_parts(d, dv, v, ld), T, nh * dv), f32)
+        ops.retention_recurrence(qk, v, ld, self.decay, cache.tensor, batch, o, nh, d, dv)
         og = rt.buffer("ret.og", (T, nh * dv))
         ops.retention_output(o, proj[:, 2 * nh * d + nh * dv:], ld, self.eps, og, nh, dv)
         return rt.linear(og, self.w_o, rt.buffer("ret.delta", (T, self.hidden)))
