@@ -101,6 +101,7 @@ _SIGNATURES = {
     "mf_head_linear_mma": [_P, c_longlong, c_int, _P, _P, c_longlong, c_int, c_int, c_int, c_int, c_int, _P,
                            c_longlong, _P],
     "mf_retention_prepare": [_P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, _P, _P, _P, _P, _P],
+    "mf_set_retention_rows": [c_int],
     "mf_retention_parts": [c_int, c_int, c_int, c_longlong],
     "mf_retention_recurrence": [_P, _P, c_int, c_longlong, _P, _P, c_longlong, _P, _P, _P, _P, c_longlong, c_int, c_int,
                                 c_int, c_int, _P],

@@ -253,6 +253,12 @@ def retention_prepare(proj: torch.Tensor, n_heads: int, dim: int, rot: int, k_sc
                                          _stream()), "retention_prepare")
 
 
+def set_retention_rows(rows: int) -> None:
+    """Rows of the state per block of the staged recurrence kernel (16, 32 or 64; for tests and measurements).
+    Results do not depend on it beyond the order in which the row groups' partial read-outs are added."""
+    check(library().mf_set_retention_rows(rows), "set_retention_rows", launches=0)
+
+
 def retention_parts(dim: int, vdim: int, v: torch.Tensor, v_ld: int) -> int:
     """How many partial read-outs ``retention_recurrence`` writes for these sizes (it spreads a head's state over
     that many groups of rows where the sizes come in whole pieces); ``retention_output`` sums them."""

@@ -138,15 +138,13 @@ retention_recurrence_kernel(const float* __restrict__ qk, const T* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------- the same, staged
-// For sizes in whole pieces (dim a multiple of 32, vdim of 16, 16-byte aligned rows): a block owns
+// For sizes in whole pieces (dim a multiple of the rows per block, vdim of 16, 16-byte aligned rows): a block owns
 // RS_ROWS rows x RT_COLS columns of S, so that a head's state is spread over dim/RS_ROWS x vdim/RT_COLS
 // blocks (an element of S depends on no other element; only the read-out sums over rows, and that sum
 // is finished by the output kernel over the row groups' partial read-outs).  The block's share of q, k
 // and v of the coming tokens arrives through a ring of cp.async stages, RS_CHUNK tokens each, so that no
 // token waits for memory.
 namespace {
-constexpr int RS_ROWS = 32;
-constexpr int RS_RPL = RS_ROWS / RT_LANES;
 constexpr int RS_CHUNK = 16;
 constexpr int RS_STAGES = 4;
 
@@ -156,13 +154,14 @@ __device__ __forceinline__ void rs_cp_async_16(void* smem, const void* gmem) {
 }
 }  // namespace
 
-template <typename T>
+template <typename T, int RS_ROWS>
 __global__ void __launch_bounds__(RT_THREADS)
 retention_recurrence_staged_kernel(const float* __restrict__ qk, const T* __restrict__ v, long long v_ld,
                                    const float* __restrict__ decay, float* __restrict__ state, long long state_stride,
                                    const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                                    const int* __restrict__ slots, float* __restrict__ o_part, long long part_stride,
                                    int n_heads, int dim, int vdim) {
+  constexpr int RS_RPL = RS_ROWS / RT_LANES;
   constexpr int V_PIECES = RT_COLS * sizeof(T) / 16;               // 16-byte pieces of a token's values
   constexpr int PIECES = 2 * RS_ROWS / 4 + V_PIECES;               // q, k, v of one token
   constexpr int TOKEN_FLOATS = 2 * RS_ROWS + RT_COLS * sizeof(T) / 4;
@@ -210,21 +209,34 @@ retention_recurrence_staged_kernel(const float* __restrict__ qk, const T* __rest
     asm volatile("cp.async.commit_group;\n" ::: "memory");
     const int stage = chunk % RS_STAGES;
     const int nb = min(RS_CHUNK, n - chunk * RS_CHUNK);
-    for (int tt = 0; tt < nb; tt++) {
-      const float* qs = &ring[stage][tt][0];
-      const float* ks = qs + RS_ROWS;
-      const float vc = to_f32<T>(reinterpret_cast<const T*>(ks + RS_ROWS)[cl]);
-      float acc = 0.f;
+    // four tokens at a time: only the state is a chain from token to token; the four read-outs' sums
+    // over the lanes of a column go through their shuffles side by side
+    for (int tt = 0; tt < nb; tt += 4) {
+      float acc[4];
 #pragma unroll
-      for (int i = 0; i < RS_RPL; i++) {
-        const int r = lane + i * RT_LANES;
-        st[i] = fmaf(g, st[i], ks[r] * vc);
-        acc = fmaf(st[i], qs[r], acc);
+      for (int u = 0; u < 4; u++) {
+        acc[u] = 0.f;
+        if (tt + u < nb) {
+          const float* qs = &ring[stage][tt + u][0];
+          const float* ks = qs + RS_ROWS;
+          const float vc = to_f32<T>(reinterpret_cast<const T*>(ks + RS_ROWS)[cl]);
+#pragma unroll
+          for (int i = 0; i < RS_RPL; i++) {
+            const int r = lane + i * RT_LANES;
+            st[i] = fmaf(g, st[i], ks[r] * vc);
+            acc[u] = fmaf(st[i], qs[r], acc[u]);
+          }
+        }
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (lane == 0) o[(long long)(t0 + chunk * RS_CHUNK + tt) * n_heads * vdim] = acc;
+#pragma unroll
+      for (int m = 1; m < RT_LANES; m <<= 1)
+#pragma unroll
+        for (int u = 0; u < 4; u++) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], m);
+      if (lane == 0) {
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+          if (tt + u < nb) o[(long long)(t0 + chunk * RS_CHUNK + tt + u) * n_heads * vdim] = acc[u];
+      }
     }
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -232,11 +244,32 @@ retention_recurrence_staged_kernel(const float* __restrict__ qk, const T* __rest
   for (int i = 0; i < RS_RPL; i++) S[(long long)(lane + i * RT_LANES) * vdim] = st[i];
 }
 
+// Rows of S per block of the staged kernel: 16, 32 or 64.  Fewer rows spread a head over more blocks,
+// more rows give a thread more of S to work on per operand it fetches.
+static int g_retention_rows = 32;
+MF_API int mf_set_retention_rows(int rows) {
+  if (rows != 16 && rows != 32 && rows != 64) return MF_ERR_BAD_ARG;
+  g_retention_rows = rows;
+  return 0;
+}
+
 // How many partial read-outs (row groups) a launch writes: retention_output sums them.
 MF_API int mf_retention_parts(int dim, int vdim, int v_dtype, long long v_ld) {
   const int vb = v_dtype == MF_F32 ? 4 : 2;
-  const bool staged = dim % RS_ROWS == 0 && vdim % RT_COLS == 0 && (v_ld * vb) % 16 == 0 && (vdim * vb) % 16 == 0;
-  return staged ? dim / RS_ROWS : 1;
+  const bool staged = dim % g_retention_rows == 0 && vdim % RT_COLS == 0 && (v_ld * vb) % 16 == 0 &&
+                      (vdim * vb) % 16 == 0;
+  return staged ? dim / g_retention_rows : 1;
+}
+
+template <typename T, int ROWS>
+static int launch_staged(const float* qk, const void* v, long long v_ld, const float* decay, float* state,
+                         long long state_stride, const int* seq_q_start, const int* seq_q_len, const int* slots,
+                         float* o_out, long long part_stride, int n_seqs, int n_heads, int dim, int vdim,
+                         cudaStream_t stream) {
+  dim3 grid(n_seqs, n_heads, (dim / ROWS) * (vdim / RT_COLS));
+  return (int)launch_dep(retention_recurrence_staged_kernel<T, ROWS>, grid, dim3(RT_THREADS), 0, stream, qk, (const T*)v,
+                         v_ld, decay, state, state_stride, seq_q_start, seq_q_len, slots, o_out, part_stride, n_heads,
+                         dim, vdim);
 }
 
 MF_API int mf_retention_recurrence(const float* qk, const void* v, int v_dtype, long long v_ld, const float* decay,
@@ -248,15 +281,18 @@ MF_API int mf_retention_recurrence(const float* qk, const void* v, int v_dtype, 
   // o_out holds mf_retention_parts(...) partial read-outs, `part_stride` floats apart
   if (mf_retention_parts(dim, vdim, v_dtype, v_ld) > 1 && ((uintptr_t)qk & 15) == 0 && ((uintptr_t)v & 15) == 0 &&
       (v_dtype == MF_F32 || v_dtype == MF_BF16)) {
-    dim3 sgrid(n_seqs, n_heads, (dim / RS_ROWS) * (vdim / RT_COLS));
     mf_count(MF_K_RETENTION_RECURRENCE);
-    if (v_dtype == MF_F32)
-      return (int)launch_dep(retention_recurrence_staged_kernel<float>, sgrid, dim3(RT_THREADS), 0, stream, qk,
-                             (const float*)v, v_ld, decay, state, state_stride, seq_q_start, seq_q_len, slots, o_out,
-                             part_stride, n_heads, dim, vdim);
-    return (int)launch_dep(retention_recurrence_staged_kernel<__nv_bfloat16>, sgrid, dim3(RT_THREADS), 0, stream, qk,
-                           (const __nv_bfloat16*)v, v_ld, decay, state, state_stride, seq_q_start, seq_q_len, slots,
-                           o_out, part_stride, n_heads, dim, vdim);
+#define RS_GO(TT, ROWS)                                                                                             \
+  return launch_staged<TT, ROWS>(qk, v, v_ld, decay, state, state_stride, seq_q_start, seq_q_len, slots, o_out,     \
+                                 part_stride, n_seqs, n_heads, dim, vdim, stream)
+#define RS_ROWS_PICK(TT)                  \
+  if (g_retention_rows == 16) RS_GO(TT, 16); \
+  if (g_retention_rows == 32) RS_GO(TT, 32); \
+  RS_GO(TT, 64)
+    if (v_dtype == MF_F32) { RS_ROWS_PICK(float); }
+    RS_ROWS_PICK(__nv_bfloat16);
+#undef RS_ROWS_PICK
+#undef RS_GO
   }
   if (mf_retention_parts(dim, vdim, v_dtype, v_ld) > 1) return MF_ERR_BAD_ARG;     // the caller sized o_out for parts
   dim3 grid(n_seqs, n_heads, (vdim + RT_COLS - 1) / RT_COLS);
