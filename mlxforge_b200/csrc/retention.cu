@@ -277,7 +277,7 @@ MF_API int mf_retention_recurrence(const float* qk, const void* v, int v_dtype, 
                                    const int* seq_q_len, const int* slots, float* o_out, long long part_stride,
                                    int n_seqs, int n_heads, int dim, int vdim, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
-  if (dim <= 0 || dim > 32 * RT_LANES || vdim <= 0 || n_heads <= 0 || n_heads > 65535) return MF_ERR_BAD_ARG;
+  if (dim <= 0 || dim > 64 * RT_LANES || vdim <= 0 || n_heads <= 0 || n_heads > 65535) return MF_ERR_BAD_ARG;
   // o_out holds mf_retention_parts(...) partial read-outs, `part_stride` floats apart
   if (mf_retention_parts(dim, vdim, v_dtype, v_ld) > 1 && ((uintptr_t)qk & 15) == 0 && ((uintptr_t)v & 15) == 0 &&
       (v_dtype == MF_F32 || v_dtype == MF_BF16)) {
@@ -307,7 +307,8 @@ MF_API int mf_retention_recurrence(const float* qk, const void* v, int v_dtype, 
   if (per <= 4) RT_LAUNCH(TT, 4);  \
   if (per <= 8) RT_LAUNCH(TT, 8);  \
   if (per <= 16) RT_LAUNCH(TT, 16); \
-  RT_LAUNCH(TT, 32)
+  if (per <= 32) RT_LAUNCH(TT, 32); \
+  RT_LAUNCH(TT, 64)
   if (v_dtype == MF_F32) { RT_PICK(float); }
   if (v_dtype == MF_BF16) { RT_PICK(__nv_bfloat16); }
 #undef RT_PICK

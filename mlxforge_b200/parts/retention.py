@@ -48,8 +48,8 @@ class Retention(Mixer):
             raise ValueError(f"retention: {len(self.decay_host)} decays for {self.n_heads} heads")
         if self.rot % 2 or self.rot > self.dim:
             raise ValueError(f"retention: rotary_dim {self.rot} must be even and at most head_dim")
-        if self.dim > 256:
-            raise ValueError(f"retention: head_dim {self.dim} is larger than the recurrence kernel's 256")
+        if self.dim > 512:
+            raise ValueError(f"retention: head_dim {self.dim} is larger than the recurrence kernel's 512")
         self.inv_f, inv_d = inverse_wavelengths(self.rot, float(p.get("rope_base", 10000.0)), runtime.device)
         self.inv_d = inv_d if runtime.precise else None
         self.decay = torch.tensor(self.decay_host, dtype=torch.float32, device=runtime.device)

@@ -290,6 +290,7 @@ RET_CASES = {
     "d64": (2, 64, 32, 64, (0.97, 0.9995)),
     "d128": (2, 128, 64, 32, (0.5, 0.999)),
     "d200": (1, 200, 24, 0, (0.98,)),
+    "d320": (1, 320, 8, 320, (0.9,)),
 }
 
 
