@@ -483,10 +483,10 @@ def test_mixed_batches_on_a_pool_where_pages_and_slots_are_used_again(models, wh
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
 def test_every_request_decoded_from_its_first_token(models, which, dtype, tmp_path):
-    """Long decoding in a batch that shrinks: the first tokens of a sequence, window edges, kept tokens and page
-    borders met token by token, decode steps replayed from graphs."""
+    """Long decoding (300 steps for C) in a batch that shrinks: the first tokens of a sequence, window edges, kept
+    tokens, page borders and the decode kernel's splits met token by token, decode steps replayed from graphs."""
     reqs = models[(which, False)][2]
     _check(models, which, False, dtype, TT.lockstep(reqs), tmp_path, max_seqs=len(reqs))
 
